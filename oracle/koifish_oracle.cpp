@@ -234,7 +234,7 @@ extern "C" int kfo_quantize(const uint16_t* w, int rows, int cols, int bits, int
  * operators and sR = 1.  How many roundings that expression has depends on how the reference is BUILT, and it is pinned against
  * the reference's own kernel compiled both ways (oracle/ref_kernels.cu, tests/test_gpu_refkernels.py):
  *   fused (default)  nvcc's default -fmad=true (implied by the reference's -use_fast_math, CMakeLists.txt:141) contracts the bf16
- *                    multiply and subtract into ONE fma.rn.bf16 on sm_90+ (SASS: HFMA2.BF16 step, k, -zero):  w = RN_bf16(step*k - zero);
+ *                    multiply and subtract into ONE fma.rn.bf16 on sm_90+:  w = RN_bf16(step*k - zero);
  *   two roundings    -fmad=false, and every pre-sm_90 build (there the bf16 operators go through fp32 with a rounding after each
  *                    operator):  p = RN_bf16(step*k) ; w = RN_bf16(p - zero).
  * ---------------------------------------------------------------------------------------------- */
