@@ -288,7 +288,7 @@ int kf_latent_expand(kf_ctx* ctx, void* out_dev, int out_f32, const float* lat_d
 /* ---- more mechanisms for stacks with a 32-bit residual (ops_f32.cu, seqmix.cu, linrec.cu, attn_bias.cu); no reference equivalents ---- */
 /* out[m] = scale * W[token[m]] as floats; out2 (optional) receives a second copy */
 int kf_embed_f32_scaled(kf_ctx* ctx, float* out_dev, float* out2_dev, const kf_tensor_desc* w, const int32_t* tokens_dev, int M, float scale);
-/* out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu; out_kind 0: bf16 bits,
+/* out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu, 4: relu; out_kind 0: bf16 bits,
  * 1: float, 2: float out += result */
 int kf_bias_act(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, const float* in_dev, int ldi, const void* bias_bf16_dev, int act, const float* mul_dev,
                 int ldm, int rows, int cols);
@@ -338,6 +338,32 @@ int kf_attn_bias_prefill(kf_ctx* ctx, void* out_bf16_dev, const void* q_bf16_dev
 int kf_attn_bias_panel(kf_ctx* ctx, void* out_bf16_dev, void* q_work_bf16_dev, const float* q_dev, int ldq, const float* gate_logit_dev, int ldg,
                        const void* cache_dev, size_t slot_stride, const void* r1_bf16_dev, const void* r2_bf16_dev, const int32_t* pos_dev,
                        const int32_t* slot_dev, int M, int H, int G, int hd, int max_seq, float scale, float t_coef, int t_every);
+
+/* ---- post-norm stacks with rotated sliding-window attention beside a scalar-decay delta rule (ops_f32.cu, attn_window.cu, linrec.cu); no
+ *      reference equivalents ---- */
+/* kf_group_rmsnorm_ex with w_add added to every weight in fp32 (1 for weights stored around zero) */
+int kf_group_rmsnorm_wadd(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, float* res_dev, float mult, const float* x_dev, int ldx, const float* gate_dev,
+                          int ldg, const void* gate_bias_bf16_dev, int gate_kind, const void* w_bf16_dev, int w_shared, float w_add, const int32_t* row_idx_dev,
+                          int rows, int dim, int groups, float eps);
+/* res[rows][dim] += rmsnorm(sa * a + sb * b) * (w_add + w) over the whole row (b may be NULL); act_out (optional) = the new res in the activation type */
+int kf_postnorm_residual(kf_ctx* ctx, float* res_dev, void* act_out_dev, int act_f32, const float* a_dev, int lda, float sa, const float* b_dev, int ldb, float sb,
+                         const void* w_bf16_dev, float w_add, int rows, int dim, float eps);
+/* kf_gated_scan with the choice of ONE decay logit per head and token (z: [H], zbias: [H]) instead of one per key channel */
+int kf_gated_scan_ex(kf_ctx* ctx, float* y_dev, int ldy, const float* q_dev, int ldq, const float* k_dev, int ldk, const float* v_dev, int ldv,
+                     const float* z_dev, int ldz, const void* zbias_bf16_dev, const void* A_log_bf16_dev, const float* beta_logit_dev, int ldb, float* state_dev,
+                     size_t state_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta,
+                     int decay_kind, float tau, int unit_qk, float unit_eps, float q_scale, int decay_per_head);
+/* x[m] = [q | k | v] floats: whole-row RMS norms of q and k (weights or NULL), rotation of the first rot_dims entries of every head by
+ * pos * inv_freq[i] (cos, sin times amp; layout 0: pairs (2i, 2i+1), 1: (i, i + rot_dims/2)); q in place, k | v into row pos % ring of the
+ * slot's cache [slot][ring][nk + nv] */
+int kf_qk_prepare(kf_ctx* ctx, float* x_dev, int ldx, int nq, int nk, int nv, int head_dim, const void* q_norm_bf16_dev, const void* k_norm_bf16_dev, float eps,
+                  int rot_dims, const double* inv_freq_dev, float amp, int layout, void* cache_dev, int cache_f32, size_t slot_stride, int ring,
+                  const int32_t* pos_dev, const int32_t* slot_dev, int M);
+/* causal grouped-query attention over the last `window` positions (<= 0: all) of a ring cache, scores capped by softcap * tanh(s / softcap)
+ * (<= 0: not capped), a per-head sink term in the softmax denominator (bf16 [H] or NULL) */
+int kf_attn_window(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const void* cache_dev, int cache_f32, size_t slot_stride,
+                   int ring, const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
+                   float softcap, int window, int max_keys_hint);
 
 #ifdef __cplusplus
 }

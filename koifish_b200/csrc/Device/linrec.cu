@@ -36,6 +36,7 @@ struct ScanArgs {
     int delta;               // 1: delta-rule write, 0: plain outer-product write
     int decay_kind;          // 0: sigmoid(z + b)^(1/tau) ; 1: exp(-exp(A_h) softplus(z + b))
     int unit_qk;             // q, k divided by sqrt(sum x^2 + unit_eps) per head
+    int z_head;              // 1: one decay per head and token (z: [H], zbias: [H]) shared by the head's key channels
     float inv_tau, q_scale, unit_eps;
 };
 
@@ -81,7 +82,8 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
                     const int tt = i / dk, n = i - tt * dk;
                     const size_t m = (size_t)(m0 + t0 + tt);
                     kv[e] = a.k[m * a.ldk + kh * dk + n], qv[e] = a.q[m * a.ldq + kh * dk + n];
-                    zv[e] = a.z[m * a.ldz + h * dk + n] + (a.zbias ? bf16_bits_to_f32(a.zbias[h * dk + n]) : 0.f);
+                    const int zi = a.z_head ? h : h * dk + n;
+                    zv[e] = a.z[m * a.ldz + zi] + (a.zbias ? bf16_bits_to_f32(a.zbias[zi]) : 0.f);
                 }
             }
 #pragma unroll
@@ -272,10 +274,11 @@ __global__ void __launch_bounds__(32 * LRU_W) kf_rglru_scan_kernel(TO* __restric
 // Matrix-state recurrence over nseq x T tokens (see the head of this file).  q, k: float rows with G kv heads of dk entries at row strides
 // ldq / ldk; v: H heads of dv entries; z: decay logits H x dk (+ bf16 bias zbias or NULL); beta_logit: H per token (delta rule only).
 // decay_kind 0: g = sigmoid(z + b)^(1/tau); 1: g = exp(-exp(A_log[h]) softplus(z + b)).  state: float [slot][H][dv][dk].
-extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z,
+// decay_per_head 1: z holds ONE logit per head and token ([H] at row stride ldz, zbias [H]); every key channel of the head decays alike.
+extern "C" int kf_gated_scan_ex(kf_ctx* ctx, float* y, int ldy, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z,
                              int ldz, const void* zbias_bf16, const void* A_log_bf16, const float* beta_logit, int ldb, float* state, size_t state_stride,
                              const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta, int decay_kind,
-                             float tau, int unit_qk, float unit_eps, float q_scale) {
+                             float tau, int unit_qk, float unit_eps, float q_scale, int decay_per_head) {
     if (!ctx || !y || !q || !k || !v || !z || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 32 * NPT, "key size <= 512, kv heads divide heads");
     KF_REQUIRE(ctx, (!delta || beta_logit) && (decay_kind == 0 ? tau > 0.f : A_log_bf16 != nullptr) && state_stride >= (size_t)H * dk * dv, "arguments");
@@ -283,7 +286,7 @@ extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int
     a.y = y, a.ldy = ldy, a.q = q, a.k = k, a.v = v, a.z = z, a.beta = beta_logit, a.ldq = ldq, a.ldk = ldk, a.ldv = ldv, a.ldz = ldz, a.ldb = ldb;
     a.zbias = (const uint16_t*)zbias_bf16, a.A_log = (const uint16_t*)A_log_bf16, a.state = state, a.state_stride = state_stride;
     a.pos = pos_dev, a.slot = slot_dev, a.T = T, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.delta = delta, a.decay_kind = decay_kind;
-    a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps;
+    a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps, a.z_head = decay_per_head ? 1 : 0;
     int R = 1;
     while (R * NPT < dk) R <<= 1;
     // up to 256 threads per CTA: the per-token chain of a warp is latency-bound and as long whatever the grid, while the staging of a pass (and
@@ -307,6 +310,14 @@ extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int
     }
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+
+extern "C" int kf_gated_scan(kf_ctx* ctx, float* y, int ldy, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv, const float* z,
+                             int ldz, const void* zbias_bf16, const void* A_log_bf16, const float* beta_logit, int ldb, float* state, size_t state_stride,
+                             const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta, int decay_kind,
+                             float tau, int unit_qk, float unit_eps, float q_scale) {
+    return kf_gated_scan_ex(ctx, y, ldy, q, ldq, k, ldk, v, ldv, z, ldz, zbias_bf16, A_log_bf16, beta_logit, ldb, state, state_stride, pos_dev, slot_dev, nseq, T, H,
+                            G, dk, dv, delta, decay_kind, tau, unit_qk, unit_eps, q_scale, 0);
 }
 
 // Real-gated linear recurrent unit over `width` channels in `blocks` equal parts.  u: float [M][ldu] (the convolved branch); gate weights

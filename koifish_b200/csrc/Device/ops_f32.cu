@@ -25,7 +25,7 @@ __global__ void kf_embed_f32_kernel(float* __restrict__ out, float* __restrict__
     }
 }
 
-// out[r][c] = act(in[r][c] + bias[c]) (* mul[r][c]) ; ACT 0: identity, 1: gelu (tanh form), 2: relu squared, 3: silu.
+// out[r][c] = act(in[r][c] + bias[c]) (* mul[r][c]) ; ACT 0: identity, 1: gelu (tanh form), 2: relu squared, 3: silu, 4: relu.
 // OUT 0: bf16 bits, 1: float, 2: out (float) += result.
 template <int ACT, int OUT>
 __global__ void kf_bias_act_kernel(void* __restrict__ out, int ldo, const float* __restrict__ in, int ldi, const uint16_t* __restrict__ bias,
@@ -36,6 +36,7 @@ __global__ void kf_bias_act_kernel(void* __restrict__ out, int ldo, const float*
         if (ACT == 1) v = gelu_tanh_f(v);
         if (ACT == 2) v = v > 0.f ? v * v : 0.f;
         if (ACT == 3) v = v * sigmoid_f(v);
+        if (ACT == 4) v = fmaxf(v, 0.f);
         if (mul) v *= mul[(size_t)r * ldm + c];
         if (OUT == 0) ((uint16_t*)out)[(size_t)r * ldo + c] = f32_to_bf16_bits(v);
         else if (OUT == 1) ((float*)out)[(size_t)r * ldo + c] = v;
@@ -68,12 +69,13 @@ __global__ void kf_depth_mix_kernel(float* __restrict__ x, float* __restrict__ h
 
 // One block per (row, group).  v = x * gatefn(g) (GATE 0: none, 1: sigmoid(g + gate_bias), 2: silu(g));  r = v / sqrt(mean_group(v^2) + eps) * w;
 // GATE 3 / 4: the gate multiplies the normed result instead, r *= sigmoid(g) / silu(g).  w_shared: one weight of group size for all groups.
-// ACC: res[row] += mult * r (fp32 residual stream)  else  out[row] = r in the activation type.
+// ACC: res[row] += mult * r (fp32 residual stream)  else  out[row] = r in the activation type.  w_add is added to every weight in
+// fp32 (1 for weights that are stored around zero).
 template <int GATE, bool ACC, typename TO>
 __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out, int ldo, float* __restrict__ res, const float* __restrict__ x, int ldx,
                                                             const float* __restrict__ gate, int ldg, const uint16_t* __restrict__ gate_bias,
                                                             const uint16_t* __restrict__ w, const int32_t* __restrict__ row_idx, int dim, int groups,
-                                                            float eps, float mult, int w_shared) {
+                                                            float eps, float mult, int w_shared, float w_add) {
     __shared__ float red[32];
     const int r = blockIdx.x, grp = blockIdx.y, gs = dim / groups;
     const int src = row_idx ? row_idx[r] : r;
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out
     ss = block_sum(ss, red);
     const float s = 1.0f / sqrtf(ss / (float)gs + eps);
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-        float o = val(i) * s * bf16_bits_to_f32(w[w_shared ? i : grp * gs + i]);
+        float o = val(i) * s * (w_add + bf16_bits_to_f32(w[w_shared ? i : grp * gs + i]));
         if (GATE == 3) o *= sigmoid_f(gr[i]);
         if (GATE == 4) {
             const float z = gr[i];
@@ -109,6 +111,35 @@ __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out
             ((uint16_t*)out)[(size_t)r * ldo + grp * gs + i] = f32_to_bf16_bits(o);
         } else {
             ((float*)out)[(size_t)r * ldo + grp * gs + i] = o;
+        }
+    }
+}
+
+// Post-norm residual step of one row:  v = sa * a + sb * b (b optional);  res += v / sqrt(mean(v^2) + eps) * (w_add + w);  the new
+// residual row is also written in the activation type (what the next sublayer's matmul reads) when act_out is given.
+template <typename TO>
+__global__ void __launch_bounds__(256) kf_postnorm_residual_kernel(float* __restrict__ res, TO* __restrict__ act_out, const float* __restrict__ a, int lda, float sa,
+                                                                   const float* __restrict__ b, int ldb, float sb, const uint16_t* __restrict__ w, float w_add,
+                                                                   int dim, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* ar = a + (size_t)r * lda;
+    const float* br = b ? b + (size_t)r * ldb : nullptr;
+    auto val = [&](int i) -> float { return br ? fmaf(sb, br[i], sa * ar[i]) : sa * ar[i]; };
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = val(i);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float* p = res + (size_t)r * dim + i;
+        const float x = *p + val(i) * s * (w_add + bf16_bits_to_f32(w[i]));
+        *p = x;
+        if (act_out) {
+            if (sizeof(TO) == 2) ((uint16_t*)act_out)[(size_t)r * dim + i] = f32_to_bf16_bits(x);
+            else ((float*)act_out)[(size_t)r * dim + i] = x;
         }
     }
 }
@@ -288,12 +319,12 @@ extern "C" int kf_embed_f32_scaled(kf_ctx* ctx, float* out, float* out2, const k
 extern "C" int kf_embed_f32(kf_ctx* ctx, float* out, const kf_tensor_desc* w, const int32_t* tokens_dev, int M) {
     return kf_embed_f32_scaled(ctx, out, nullptr, w, tokens_dev, M, 1.f);
 }
-// out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu; out_kind 0: bf16 bits,
+// out[rows][ldo] = act(in[rows][ldi] + bias) (* mul); act 0: none, 1: gelu (tanh form), 2: relu squared, 3: silu, 4: relu; out_kind 0: bf16 bits,
 // 1: float, 2: float out += result.  bias: bf16 [cols] or NULL; mul: float [rows][ldm] or NULL.
 extern "C" int kf_bias_act(kf_ctx* ctx, void* out, int out_kind, int ldo, const float* in, int ldi, const void* bias_bf16, int act, const float* mul, int ldm,
                            int rows, int cols) {
     if (!ctx || !out || !in) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, rows >= 1 && cols >= 1 && act >= 0 && act <= 3 && out_kind >= 0 && out_kind <= 2, "act / out kind");
+    KF_REQUIRE(ctx, rows >= 1 && cols >= 1 && act >= 0 && act <= 4 && out_kind >= 0 && out_kind <= 2, "act / out kind");
     dim3 grid(std::min(64, (cols + 255) / 256), rows);
     const uint16_t* b = (const uint16_t*)bias_bf16;
 #define KF_BA(A, O) kf_bias_act_kernel<A, O><<<grid, 256, 0, ctx->stream>>>(out, ldo, in, ldi, b, mul, ldm, cols)
@@ -301,7 +332,8 @@ extern "C" int kf_bias_act(kf_ctx* ctx, void* out, int out_kind, int ldo, const 
     if (act == 0) KF_BA_O(0);
     else if (act == 1) KF_BA_O(1);
     else if (act == 2) KF_BA_O(2);
-    else KF_BA_O(3);
+    else if (act == 3) KF_BA_O(3);
+    else KF_BA_O(4);
 #undef KF_BA_O
 #undef KF_BA
     KF_LAUNCH_CHECK(ctx);
@@ -327,16 +359,17 @@ extern "C" int kf_depth_mix(kf_ctx* ctx, float* x, float* hist, size_t hist_stri
 // gate_kind 0: none; 1: x * sigmoid(gate + gate_bias); 2: x * silu(gate).  out_kind 0: bf16 bits [rows][ldo]; 1: float [rows][ldo];
 // 2: res[rows][dim] += mult * result (out is ignored).  row_idx (device, optional): source row of each output row.
 // gate_kind 3 / 4: sigmoid(gate) / silu(gate) multiply the normed result; w_shared: the weight has dim / groups entries, used by every group.
-extern "C" int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
-                                   const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, const int32_t* row_idx, int rows, int dim,
-                                   int groups, float eps) {
+// w_add: added to every weight in fp32 (1 for weights stored around zero, 0 for plain weights).
+extern "C" int kf_group_rmsnorm_wadd(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
+                                     const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, float w_add, const int32_t* row_idx, int rows,
+                                     int dim, int groups, float eps) {
     if (!ctx || !x || !w_bf16) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, rows >= 1 && dim >= 1 && groups >= 1 && dim % groups == 0, "groups must divide dim");
     KF_REQUIRE(ctx, gate_kind >= 0 && gate_kind <= 4 && (gate_kind == 0 || gate) && out_kind >= 0 && out_kind <= 2 && (out_kind == 2 ? res != nullptr : out != nullptr),
                "gate / out kind");
     dim3 grid(rows, groups);
     const uint16_t *gb = (const uint16_t*)gate_bias_bf16, *w = (const uint16_t*)w_bf16;
-#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult, w_shared)
+#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult, w_shared, w_add)
     if (out_kind == 2) {
         if (gate_kind == 0) KF_GN(0, true, float);
         else if (gate_kind == 1) KF_GN(1, true, float);
@@ -360,11 +393,30 @@ extern "C" int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out, int out_kind, int ldo
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
+extern "C" int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
+                                   const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, const int32_t* row_idx, int rows, int dim,
+                                   int groups, float eps) {
+    return kf_group_rmsnorm_wadd(ctx, out, out_kind, ldo, res, mult, x, ldx, gate, ldg, gate_bias_bf16, gate_kind, w_bf16, w_shared, 0.f, row_idx, rows, dim,
+                                 groups, eps);
+}
 extern "C" int kf_group_rmsnorm(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
                                 const void* gate_bias_bf16, int gate_kind, const void* w_bf16, const int32_t* row_idx, int rows, int dim, int groups,
                                 float eps) {
     if (gate_kind > 2) return KF_ERR_BAD_ARG;
     return kf_group_rmsnorm_ex(ctx, out, out_kind, ldo, res, mult, x, ldx, gate, ldg, gate_bias_bf16, gate_kind, w_bf16, 0, row_idx, rows, dim, groups, eps);
+}
+// res[rows][dim] += rmsnorm(sa * a + sb * b) * (w_add + w);  act_out (optional, [rows][dim] in the activation type) = the new res.
+// b may be NULL (one branch).  The norm runs over the whole row.
+extern "C" int kf_postnorm_residual(kf_ctx* ctx, float* res, void* act_out, int act_f32, const float* a, int lda, float sa, const float* b, int ldb, float sb,
+                                    const void* w_bf16, float w_add, int rows, int dim, float eps) {
+    if (!ctx || !res || !a || !w_bf16) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && dim >= 1, "shape");
+    if (act_f32)
+        kf_postnorm_residual_kernel<float><<<rows, 256, 0, ctx->stream>>>(res, (float*)act_out, a, lda, sa, b, ldb, sb, (const uint16_t*)w_bf16, w_add, dim, eps);
+    else
+        kf_postnorm_residual_kernel<uint16_t><<<rows, 256, 0, ctx->stream>>>(res, (uint16_t*)act_out, a, lda, sa, b, ldb, sb, (const uint16_t*)w_bf16, w_add, dim, eps);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
 }
 extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size_t n) {
     if (!ctx || !out_bf16 || !in) return KF_ERR_BAD_ARG;

@@ -38,6 +38,16 @@ struct MIXER_CARD {
     int qt_every  = 0;
     // real-gated linear recurrent unit beside the attention of a "parallel" mixer
     int lru_width = 0, lru_blocks = 1, lru_conv = 1;
+    // rotated sliding-window attention: keys of the last `window` positions (0: all), scores capped by softcap * tanh(s / softcap) (0: not),
+    // a sink term per head in the softmax, frequencies stretched between two wavelengths (yarn_factor 0: plain rot_base^(-2i/rot_dims))
+    int window = 0;
+    float softcap = 0.f;
+    bool sink = false;
+    double yarn_factor = 0.0, yarn_original = 0.0, yarn_fast = 0.0, yarn_slow = 0.0;
+    // two mixers side by side that read the same input (Sedotar's "parallel"): this card is the left one, `right` the other; the result is
+    // left_scale * left + right_scale * right
+    std::shared_ptr<MIXER_CARD> right;
+    float left_scale = 1.f, right_scale = 1.f;
 };
 struct MOE_CARD {
     bool present = false;
@@ -164,6 +174,7 @@ struct SeqStateCache {
         size_t state_stride = 0;
         float* tail = nullptr;     // [max_batch][tail_stride]
         size_t tail_stride = 0;
+        int ring = 0;              // > 0: the rows of a slot are a ring of this many positions (position p in row p % ring), not max_seq rows
     };
     std::vector<Layer> layers;
     int max_batch = 1, max_seq = 0;
@@ -186,6 +197,7 @@ struct ARCH_ENTRY {
 const ARCH_ENTRY* FindArch(const std::string& name);
 const ARCH_ENTRY* SipazenArch();  // Sipazen.cpp
 const ARCH_ENTRY* KivoraxArch();  // Kivorax.cpp
+const ARCH_ENTRY* SedotarArch();  // Sedotar.cpp
 
 // ---- the model ------------------------------------------------------------------------------------------------------------
 struct Fish {
