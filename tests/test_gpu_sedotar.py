@@ -1,0 +1,314 @@
+"""GPU tests of the Sedotar stack against the plain float64 restatement in sedotar_ref.py, on small random models made here.
+
+Gates: with gpt.compute_dtype = float32 the logits agree to 2e-4 (rms of the difference, mean removed, over the rms of the logits);
+in bf16 nine rows in ten to 6e-2.  Weights are drawn on the bf16 grid, so both sides hold the same numbers.  Where random weights would
+hide a fault they are shaped: query norm weights scaled up so that one key wins the softmax (a window one position off, a key of the
+wrong ring row, a missing cap then moves the logits far), sinks raised so that leaving them out shows, decays set slow so that the first
+tokens still matter hundreds of steps later.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import koifish_b200 as kf
+import sedotar_ref as ref
+from sedotar_models import bf16_grid, bits, config, layer, left, right, tokens, weights
+from st_util import write_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {True: 2e-4, False: 6e-2}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = kf.Context(0)
+    yield c
+    c.close()
+
+
+def build(ctx, cfg, W, f32, max_seq=256, slots=2, panel=64, logit_rows=None):
+    gpt = {"max_seq_len": max_seq, "max_batch": slots, "max_prefill": panel, "logit_rows": logit_rows or panel}
+    if f32:
+        gpt["compute_dtype"] = "float32"
+    m = kf.Model(ctx, {"hf_config": cfg, "gpt": gpt})
+    assert sorted(m.tensor_names()) == sorted(W.keys())
+    for k, v in W.items():
+        m.set_tensor(k, bits(v).reshape(-1, v.shape[-1]) if v.dim() > 1 else bits(v))
+    return m
+
+
+def rel(got, want, q=1.0):
+    """largest (q = 1) or q-quantile row error: rms of the difference, mean removed, over the rms of the wanted logits"""
+    d = np.asarray(got, dtype=np.float64) - np.asarray(want, dtype=np.float64)
+    d = d - d.mean(-1, keepdims=True)
+    w = np.asarray(want, dtype=np.float64)
+    w = w - w.mean(-1, keepdims=True)
+    return float(np.quantile(np.atleast_1d(np.sqrt((d ** 2).mean(-1))), q) / np.sqrt((w ** 2).mean()))
+
+
+def close(got, want, f32):
+    if f32:
+        return rel(got, want) < TOL[True]
+    return rel(got, want, 0.9) < TOL[False] and rel(got, want) < 0.5
+
+
+def oracle(cfg, W, toks):
+    return ref.forward(cfg, W, list(toks)).numpy()
+
+
+def run_cut(model, toks, cuts, slot=0):
+    """feed toks in portions of the given sizes (the rest one by one); fp32 logits of every position"""
+    out, at = [], 0
+    sizes = list(cuts)
+    while at < len(toks):
+        n = sizes.pop(0) if sizes else 1
+        n = min(n, len(toks) - at)
+        lg, _ = model.forward_rows(toks[at:at + n], at, slot=slot, rows=list(range(n)))
+        out.append(lg)
+        at += n
+    return np.concatenate(out)
+
+
+FULL = [layer(),
+        layer(left(heads=2, kv_heads=2, dim=8, vdim=40, conv=1, window=5, softcap=0, rot_dims=8, scaling=False), right(heads=2, kv_heads=1, dim=40, vdim=6, conv=1),
+              ff=0),
+        layer(left(heads=6, kv_heads=1, dim=16, vdim=8, conv=4, window=33, rot_dims=4, base=50.0), right(heads=1, kv_heads=1, dim=8, vdim=8, conv=4), ff=24,
+              left_scale=1.0, right_scale=1.0),
+        layer(left(heads=3, kv_heads=3, dim=10, vdim=10, conv=2, window=0, rot_dims=0), right(heads=6, kv_heads=2, dim=12, vdim=9, conv=3), ff=16)]
+
+
+# ------------------------------------------------------------------------------------------------------------ each mechanism alone
+@pytest.mark.parametrize("f32", [True, False])
+@pytest.mark.parametrize("ly", [
+    layer(ff=0),
+    layer(ff=0, left_scale=1.0, right_scale=0.0),                                            # the attention alone
+    layer(ff=0, left_scale=0.0, right_scale=1.0),                                            # the delta rule alone
+    layer(left(heads=3, kv_heads=3, dim=8, vdim=8, conv=1, rot_dims=8), ff=0, right_scale=0.0),              # no grouping, one tap, every entry rotated
+    layer(left(heads=1, kv_heads=1, dim=6, vdim=70, window=1, rot_dims=2, scaling=False), ff=0, right_scale=0.0),  # one head, a window of the token itself, wide values
+    layer(left(window=0, softcap=0, rot_dims=0), ff=0, right_scale=0.0),                     # all keys, no cap, no rotation: plain attention with a sink
+    layer(left(scaling={"factor": 16.0, "original": 20, "fast": 2.0, "slow": 0.5}, rot_dims=12, base=200.0), ff=0, right_scale=0.0),  # the ramp inside the table
+    layer(r=right(heads=3, kv_heads=3, dim=40, vdim=7, conv=1), ff=0, left_scale=0.0),       # key size over several lanes, one tap
+    layer(r=right(heads=1, kv_heads=1, dim=8, vdim=8, conv=5), ff=0, left_scale=0.0),        # one head, all sizes equal
+    layer(r=right(heads=6, kv_heads=2, dim=16, vdim=33), ff=0, left_scale=0.0),              # three value heads per key head
+    layer(ff=56, left_scale=0.0, right_scale=1.0),
+], ids=["pair", "left", "right", "left_plain_heads", "left_one_head_window1", "left_no_window_cap_rot", "left_ramp", "right_wide_key", "right_one_head",
+        "right_grouped", "ff"])
+def test_single_layer_prompt(ctx, ly, f32):
+    cfg = config([ly], width=32)
+    W = weights(cfg, seed=3)
+    toks = tokens(37, cfg["vocab"], 1)
+    m = build(ctx, cfg, W, f32)
+    got, _ = m.forward_rows(toks, 0, rows=list(range(len(toks))))
+    assert close(got, oracle(cfg, W, toks), f32)
+    m.close()
+
+
+def test_norm_weights_are_one_plus(ctx):
+    """norm weights far from zero, an embedding scale far from 1: a norm applied as w instead of 1 + w, or a scaled head, shows"""
+    cfg = config([layer(ff=24)], width=32, scale=11.0)
+    W = weights(cfg, seed=4)
+    for k in ("final.norm", "l0.norm1", "l0.norm2"):
+        W[k] = bf16_grid(W[k] * 3.0 - 0.5)
+    toks = tokens(20, cfg["vocab"], 2)
+    m = build(ctx, cfg, W, True)
+    assert rel(run_cut(m, toks, [9, 2]), oracle(cfg, W, toks)) < TOL[True]
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ whole stacks
+@pytest.mark.parametrize("f32", [True, False])
+def test_stack_prompt_and_decode(ctx, f32):
+    """a prompt in one step, then token by token: both equal the oracle; the first tokens of a sequence decoded one by one as well"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=5)
+    toks = tokens(90, cfg["vocab"], 2)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, f32)
+    assert close(run_cut(m, toks, [64, 26]), want, f32)          # two panels
+    assert close(run_cut(m, toks, [50]), want, f32)              # 50 at once, 40 decoded (graph replay from the second step on)
+    assert close(run_cut(m, toks[:12], []), want[:12], f32)       # from the very first token one by one
+    m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_wide_panels_and_tuned_matmul_widths(ctx, f32):
+    """width 128, extents that are multiples of 16, panels of up to 192 tokens: in bf16 the projections run on the tensor-core kernels"""
+    cfg = config([layer(left(heads=4, kv_heads=2, dim=32, vdim=16, window=70, rot_dims=16), right(heads=4, kv_heads=2, dim=16, vdim=32), ff=256),
+                  layer(left(heads=2, kv_heads=1, dim=64, vdim=64, window=200, rot_dims=64), right(heads=2, kv_heads=2, dim=64, vdim=64), ff=0)], width=128, vocab=160)
+    W = weights(cfg, seed=14)
+    toks = tokens(230, cfg["vocab"], 15)
+    m = build(ctx, cfg, W, f32, panel=192, logit_rows=192)
+    assert close(run_cut(m, toks, [192, 17, 2]), oracle(cfg, W, toks), f32)
+    m.close()
+
+
+def test_portions_of_many_sizes(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=6)
+    toks = tokens(131, cfg["vocab"], 3)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, True)
+    for cuts in ([2, 2, 3, 2, 64, 2, 31, 2, 17], [1, 2, 1, 63, 64, 1], [7] * 19, [64, 64, 2], [3, 1, 1, 2, 5, 64, 2, 2, 2, 40]):
+        assert rel(run_cut(m, toks, cuts), want) < TOL[True], cuts
+    m.close()
+
+
+def test_slots_reused_and_interleaved(ctx):
+    """two requests advance alternately in two slots; a released slot is taken by a new request and nothing of the old one shows"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=7)
+    a, b, c = tokens(70, cfg["vocab"], 4), tokens(45, cfg["vocab"], 5), tokens(20, cfg["vocab"], 6)
+    wa, wb, wc = oracle(cfg, W, a), oracle(cfg, W, b), oracle(cfg, W, c)
+    m = build(ctx, cfg, W, True, slots=2)
+    sa, sb = m.acquire_slot(), m.acquire_slot()
+    assert {sa, sb} == {0, 1}
+    with pytest.raises(kf.KoifishError):
+        m.acquire_slot()
+    ga, gb, ia, ib = [], [], 0, 0
+    for na, nb in [(30, 2), (1, 20), (2, 1), (37, 22)]:
+        lg, _ = m.forward_rows(a[ia:ia + na], ia, slot=sa, rows=list(range(na)))
+        ga.append(lg), (ia := ia + na)
+        lg, _ = m.forward_rows(b[ib:ib + nb], ib, slot=sb, rows=list(range(nb)))
+        gb.append(lg), (ib := ib + nb)
+    assert rel(np.concatenate(ga), wa) < TOL[True] and rel(np.concatenate(gb), wb) < TOL[True]
+    m.release_slot(sa)
+    with pytest.raises(kf.KoifishError):
+        m.release_slot(sa)
+    sc = m.acquire_slot()
+    assert sc == sa  # the slot that held the 70-token request: state, convolution inputs and ring rows still in place
+    assert rel(run_cut(m, c, [3, 2], slot=sc), wc) < TOL[True]
+    m.close()
+
+
+def test_batched_decode_of_unequal_requests(ctx):
+    """three sequences of different lengths take one token each in one step: every row equals the sequence run alone"""
+    cfg = config(FULL)
+    W = weights(cfg, seed=8)
+    seqs = [tokens(n, cfg["vocab"], 10 + n) for n in (41, 7, 18)]
+    m = build(ctx, cfg, W, True, slots=3)
+    for s, t in enumerate(seqs):
+        m.forward_rows(t[:-4], 0, slot=s)
+    for k in range(4, 0, -1):
+        lg, _ = m.forward_batch([t[len(t) - k] for t in seqs], [len(t) - k for t in seqs])
+        for s, t in enumerate(seqs):
+            assert rel(lg[s], oracle(cfg, W, t)[len(t) - k]) < TOL[True], (s, k)
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ shaped weights
+def edited(cfg, fn):
+    c = json.loads(json.dumps(cfg))
+    fn(c["layers"][0]["mixer"]["left"])
+    return c
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_window_edges_cap_and_sink(ctx, f32):
+    """a peaked softmax (query norm weights x 12) over a window of 23 positions, sinks near the largest scores, a cap that bites: the key that
+    wins sits anywhere in the window, often at its far edge.  The oracle itself shows that each of these matters: a window one position
+    longer or shorter, the sink left out, the cap left out or the stretch of the frequencies left out move the logits far beyond the gate.
+    The framework then has to match in prompt panels (edges inside a panel and across panels), in small portions and in decoding, over
+    more than five turns of the ring (23 + 64 - 1 rows)."""
+    cfg = config([layer(left(heads=4, kv_heads=2, dim=16, vdim=12, window=23, softcap=6.0, rot_dims=12, base=100.0), ff=0, left_scale=1.0, right_scale=0.3),
+                  layer(left(window=40), ff=24)])
+    W = weights(cfg, seed=9, q_gain=12.0, sink=5.0)
+    toks = tokens(520, cfg["vocab"], 7)
+    want = oracle(cfg, W, toks)
+    gate = 5 * TOL[f32]
+    assert rel(oracle(edited(cfg, lambda a: a["mask"].update(size=24)), W, toks), want) > gate
+    assert rel(oracle(edited(cfg, lambda a: a["mask"].update(size=22)), W, toks), want) > gate
+    assert rel(oracle(edited(cfg, lambda a: a.pop("softcap")), W, toks), want) > gate
+    assert rel(oracle(edited(cfg, lambda a: a["rot"].pop("scaling")), W, toks), want) > gate
+    assert rel(oracle(cfg, {k: v for k, v in W.items() if k != "l0.mix.left.sink"}, toks), want) > gate
+    m = build(ctx, cfg, W, f32, max_seq=640)
+    assert m.info.kv_bytes < 2 * 640 * (56 + 44) * (4 if f32 else 2) // 3  # rings of window + panel - 1 rows (56 and 44 entries), not max_seq rows
+    got = run_cut(m, toks, [64, 64, 23, 22, 24, 2, 2, 3, 64, 1, 64, 29])  # 362 in portions, then 158 decoded one by one
+    assert close(got, want, f32)
+    m.close()
+
+
+def test_long_decoding_through_the_ring(ctx):
+    """three tokens of prompt, then 300 decoded one by one with a window of 7 (ring of 7 + 64 - 1 rows: four turns), all positions checked"""
+    cfg = config([layer(left(window=7), ff=16), layer(left(window=64, rot_dims=12, dim=12), ff=0)])
+    W = weights(cfg, seed=10, q_gain=6.0)
+    toks = tokens(303, cfg["vocab"], 8)
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [3]), oracle(cfg, W, toks)) < TOL[True]
+    m.close()
+
+
+def test_slow_decay_keeps_the_first_tokens(ctx):
+    """decays close to 1: the state after 300 tokens still holds the first ones, long after they left every window; cutting the sequence
+    anywhere, also inside the convolutions' reach of a cut, leaves the logits alone"""
+    cfg = config([layer(left(window=16), right(conv=4), ff=0, left_scale=0.3, right_scale=1.0), layer(ff=24)])
+    W = weights(cfg, seed=10, a_log=-7.0, dt_bias=-2.0)
+    toks = tokens(300, cfg["vocab"], 8)
+    want = oracle(cfg, W, toks)
+    other = list(toks)
+    other[0] = (toks[0] + 1) % cfg["vocab"]
+    assert rel(oracle(cfg, W, other)[-1], want[-1]) > 10 * TOL[True]  # the last logits do depend on the first token
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [64, 64, 1, 2, 1, 1, 3, 64, 2]), want) < TOL[True]  # ... then 98 decoded one by one
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ entry points
+def test_greedy_generation(ctx):
+    cfg = config(FULL)
+    W = weights(cfg, seed=11)
+    prompt = tokens(70, cfg["vocab"], 9)  # longer than a panel
+    seq = list(prompt)
+    for _ in range(12):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    m = build(ctx, cfg, W, True)
+    out, why = m.generate(prompt, 12)
+    assert out == seq[len(prompt):] and why == 2
+    m.close()
+
+
+def test_command_line_on_a_checkpoint_folder(ctx, tmp_path):
+    """config.json + model.safetensors on disk -> `generate` and `trace` of the command line, both number formats; optional keys left out of
+    the file (kv_heads, scale, the branch scales) take their defaults"""
+    cfg = config(FULL[:3])
+    for ly in cfg["layers"]:
+        ly["mixer"]["left_scale"] = ly["mixer"]["right_scale"] = 1.0
+    cfg["layers"][1]["mixer"]["left"]["scale"] = 8 ** -0.5
+    W = weights(cfg, seed=12)
+    disk = json.loads(json.dumps(cfg))
+    for ly in disk["layers"]:
+        ly["mixer"].pop("left_scale"), ly["mixer"].pop("right_scale")
+    disk["layers"][1]["mixer"]["left"].pop("scale"), disk["layers"][1]["mixer"]["left"].pop("kv_heads")
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(disk))
+    write_safetensors(str(d / "model.safetensors"), [(k, "BF16", bits(v).reshape(v.shape)) for k, v in W.items()])
+    a, b = tokens(75, cfg["vocab"], 13), tokens(9, cfg["vocab"], 14)
+    wa, wb = oracle(cfg, W, a), oracle(cfg, W, b)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:70], "want": [0, 5, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[70:72], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[72:], "want": [2, 1]}], "end": ["x"]},
+             {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [8]}], "end": ["y"]}]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / ("out_" + dtype)
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(d), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+        assert not (out / "1.f32").exists()
+        f = lambda n: np.fromfile(str(out / ("%d.f32" % n)), dtype="<f4").reshape(-1, cfg["vocab"])
+        assert close(np.concatenate([f(0), f(2), f(3)]), np.concatenate([wa[[0, 5, 69]], wa[[74, 73]], wb[[8]]]), dtype == "float32")
+    r = subprocess.run([sys.executable, "-m", "koifish_b200.cli", "generate", "--model", str(d), "--ids", ",".join(map(str, b)), "--max-new-tokens", "5"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    seq = list(b)
+    for _ in range(5):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    got = json.loads(r.stdout.strip().splitlines()[-1])["tokens"]
+    assert len(got) == 5 and got[0] == seq[len(b)]  # bf16 serving: the first token is far from a tie; later ones may legitimately differ
