@@ -355,15 +355,19 @@ int kf_gated_scan_ex(kf_ctx* ctx, float* y_dev, int ldy, const float* q_dev, int
                      int decay_kind, float tau, int unit_qk, float unit_eps, float q_scale, int decay_per_head);
 /* x[m] = [q | k | v] floats: whole-row RMS norms of q and k (weights or NULL), rotation of the first rot_dims entries of every head by
  * pos * inv_freq[i] (cos, sin times amp; layout 0: pairs (2i, 2i+1), 1: (i, i + rot_dims/2)); q in place, k | v into row pos % ring of the
- * slot's cache [slot][ring][nk + nv] */
+ * slot's cache [slot][ring][nk + nv]; q_bf16_out_dev (optional): a bf16 copy of the finished q, [M][nq] */
 int kf_qk_prepare(kf_ctx* ctx, float* x_dev, int ldx, int nq, int nk, int nv, int head_dim, const void* q_norm_bf16_dev, const void* k_norm_bf16_dev, float eps,
                   int rot_dims, const double* inv_freq_dev, float amp, int layout, void* cache_dev, int cache_f32, size_t slot_stride, int ring,
-                  const int32_t* pos_dev, const int32_t* slot_dev, int M);
+                  void* q_bf16_out_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M);
 /* causal grouped-query attention over the last `window` positions (<= 0: all) of a ring cache, scores capped by softcap * tanh(s / softcap)
  * (<= 0: not capped), a per-head sink term in the softmax denominator (bf16 [H] or NULL) */
 int kf_attn_window(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const void* cache_dev, int cache_f32, size_t slot_stride,
                    int ring, const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
                    float softcap, int window, int max_keys_hint);
+/* the same attention for a panel of M consecutive tokens of one slot on the tensor cores (bf16 ring cache, dk == dv in {64, 128}; attention.cu) */
+int kf_attn_window_prefill(kf_ctx* ctx, void* out_bf16_dev, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, int ring,
+                           const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale,
+                           float softcap, int window);
 
 #ifdef __cplusplus
 }

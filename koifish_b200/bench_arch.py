@@ -1,6 +1,8 @@
-"""Prefill and decode throughput of a hybrid stack (bench.py --compare-arch sipazen | kivorax) beside the closest existing models at equal
-width, depth and active feed-forward width: Sipazen beside Qwen3; Kivorax beside Sipazen (the other recurrence + attention + experts
-stack of this runtime) and Qwen3.  All bf16 with random weights.  One JSON line per (model, size).
+"""Prefill and decode throughput of a hybrid stack (bench.py --compare-arch sipazen | kivorax | sedotar) beside the closest existing models
+at equal width, depth and active feed-forward width: Sipazen beside Qwen3; Kivorax beside Sipazen (the other recurrence + attention +
+experts stack of this runtime) and Qwen3; Sedotar (sliding-window attention beside a delta rule, dense feed-forward) beside Kivorax with
+dense feed-forwards (delta-rule layers and attention layers alternating) and Qwen3.  All bf16 with random weights.  One JSON line per
+(model, size).
 
     prefill: a prompt of --prompt tokens through the model's own step function in panels, timed with CUDA events after 3 warm-up prompts
     decode : the device-resident greedy loop (one CUDA-graph replay per token) at context --prompt, after W warm-up tokens
@@ -16,17 +18,20 @@ PRESETS = {
               ssm=dict(heads=32, vdim=64, state=64, groups=1, norm_groups=1, conv=4),
               att=dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256),
               moe=dict(experts=16, top=2, ff=512, shared=1024),
-              kvx=dict(pattern="ddgpdg", heads=8, dim=64, rank=32)),
+              kvx=dict(pattern="ddgpdg", heads=8, dim=64, rank=32),
+              sdt=dict(heads=8, kv_heads=2, window=1024, ff=4096)),
     "m": dict(width=2048, vocab=65536, pattern="mmammama",
               ssm=dict(heads=64, vdim=64, state=128, groups=8, norm_groups=8, conv=4),
               att=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512),
               moe=dict(experts=64, top=6, ff=1408, shared=2816),
-              kvx=dict(pattern="ddgpddgp", heads=16, dim=64, rank=64)),
+              kvx=dict(pattern="ddgpddgp", heads=16, dim=64, rank=64),
+              sdt=dict(heads=16, kv_heads=4, window=1024, ff=8192)),
     "l": dict(width=4096, vocab=65536, pattern="mmam",
               ssm=dict(heads=128, vdim=64, state=128, groups=8, norm_groups=8, conv=4),
               att=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512),
               moe=dict(experts=32, top=4, ff=2048, shared=4096),
-              kvx=dict(pattern="dgpd", heads=32, dim=64, rank=64)),
+              kvx=dict(pattern="dgpd", heads=32, dim=64, rank=64),
+              sdt=dict(heads=32, kv_heads=8, window=2048, ff=16384)),
 }
 
 
@@ -62,6 +67,33 @@ def kivorax_config(p):
     return {"architecture": "Kivorax", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "token_side": {"dim": 64}, "layers": layers}
 
 
+def sedotar_config(p):
+    """every layer: attention (head size 128, 4 query heads per kv head, half of each head rotated, window, cap 30, sink) beside the delta
+    rule (as many value heads of 128, half as many key heads of 64), then the relu-gated feed-forward"""
+    w, d = p["width"], p["sdt"]
+    lf = dict(heads=d["heads"], kv_heads=d["kv_heads"], dim=128, vdim=128, conv=4, scale=128 ** -0.5, softcap=30.0, mask=dict(size=d["window"]),
+              rot=dict(base=1e6, dims=64, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    rt = dict(heads=d["heads"], kv_heads=d["heads"] // 2, dim=64, vdim=128, conv=4)
+    ly = {"type": "parallel", "mixer": {"left": lf, "right": rt, "left_scale": 0.7, "right_scale": 0.7}, "mlp": {"kind": "dense", "ff": d["ff"]}}
+    return {"architecture": "Sedotar", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": [ly] * len(p["pattern"])}
+
+
+def kivorax_dense_config(p):
+    """Kivorax at the size of sedotar_config: delta-rule layers and attention (+ LRU) layers alternating, a dense feed-forward of the same
+    width in every layer, no side input"""
+    w, d = p["width"], p["sdt"]
+    layers = []
+    for i in range(len(p["pattern"])):
+        if i % 2 == 0:
+            mixer, typ = dict(heads=d["heads"], kv_heads=d["heads"] // 2, dim=64, vdim=128, conv=4, a_rank=64, g_rank=64), "channel_delta"
+        else:
+            mixer = dict(left=dict(heads=d["heads"], kv_heads=d["kv_heads"], dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.4, every=512)),
+                         right=dict(width=w, blocks=d["heads"], conv=4))
+            typ = "parallel"
+        layers.append({"type": typ, "mixer": mixer, "mlp": {"kind": "dense", "ff": d["ff"]}})
+    return {"architecture": "Kivorax", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": layers}
+
+
 def kivorax_fixups(model, cfg):
     """tensors that random normal weights would make meaningless: positive distance-penalty numbers, depth weights (0, .., 0, 1), unit norms"""
     import numpy as np
@@ -89,16 +121,21 @@ def run(args, ctx, stream):
         n_layer = len(p["pattern"])
         ff_active = p["moe"]["top"] * p["moe"]["ff"] + p["moe"]["shared"]
         cfgs = {}
+        gpt = {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel}
+        if args.compare_arch == "sedotar":
+            kcfg = kivorax_dense_config(p)
+            ff_active = p["sdt"]["ff"]
+            cfgs["sedotar"] = {"hf_config": sedotar_config(p), "gpt": dict(gpt), "init": {"sigma": 0.02, "norm_sigma": 0.02}}
+            cfgs["kivorax"] = {"hf_config": kcfg, "gpt": dict(gpt), "init": {"sigma": 0.02, "norm_sigma": 0.02}}
         if args.compare_arch == "kivorax":
             kcfg = kivorax_config(p)
             cfgs["kivorax"] = {"hf_config": kcfg, "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
                                "init": {"sigma": 0.02, "norm_sigma": 0.02}}
-        cfgs.update({
-            "sipazen": {"hf_config": sipazen_config(p), "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
-                        "init": {"sigma": 0.02, "norm_sigma": 0.02}},
-            "qwen3": kf.qwen3_config(n_layer, p["width"], (ff_active + 127) // 128 * 128, p["width"] // 128, max(1, p["width"] // 512), 128, p["vocab"], None, False,
-                                     P + args.steps + args.warmup + 64, 1, 42, 1e6, max_prefill=panel),
-        })
+        if args.compare_arch != "sedotar":
+            cfgs["sipazen"] = {"hf_config": sipazen_config(p), "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
+                               "init": {"sigma": 0.02, "norm_sigma": 0.02}}
+        cfgs["qwen3"] = kf.qwen3_config(n_layer, p["width"], (ff_active + 127) // 128 * 128, p["width"] // 128, max(1, p["width"] // 512), 128, p["vocab"], None, False,
+                                        P + args.steps + args.warmup + 64, 1, 42, 1e6, max_prefill=panel)
         for name, cfg in cfgs.items():
             model = kf.Model(ctx, cfg)
             model.init_random()
@@ -135,7 +172,7 @@ def run(args, ctx, stream):
             torch.cuda.synchronize()
             decode_ms = e0.elapsed_time(e1) / args.steps
             info = model.info
-            line = {"bench": "arch-compare", "model": name, "size": size, "width": p["width"], "layers": n_layer, "pattern": p["kvx"]["pattern"] if name == "kivorax" else p["pattern"],
+            line = {"bench": "arch-compare", "model": name, "size": size, "width": p["width"], "layers": n_layer, "pattern": p["pattern"] if name in ("sipazen", "qwen3") else "".join(ly["type"][0] for ly in cfg["hf_config"]["layers"]),
                     "weight_gb": round(info.weight_bytes / 1e9, 3), "prompt": P, "panel": panel,
                     "prefill_tok_s": round(P / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3), "prefill_launches": prefill_launches,
                     "decode_tok_s": round(1e3 / decode_ms, 1), "decode_ms": round(decode_ms, 4), "decode_launches_per_token": (ctx.launches - l0) / args.steps,

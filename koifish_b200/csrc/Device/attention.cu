@@ -554,12 +554,20 @@ struct PfBias {
     size_t slot_stride;       // elements per slot
     int kv_stride;            // elements between consecutive positions
     float scale;
+    // MODE 2 (sliding window over a ring of rows): position t sits in row t % ring; a query at p sees p - window < t <= p; the score is
+    // capped, softcap * tanh(s / softcap) (softcap <= 0: not); sink (bf16 [n_head] or NULL) joins the softmax denominator
+    int ring, window;
+    float softcap;
+    const uint16_t* sink;
 };
-template <int HD, int BKV, bool BIAS>
+// MODE 0: Qwen3's plain causal attention over separate K and V caches.  MODE 1: see above.  MODE 2: the side-by-side rows and hi + lo
+// softmax weights of MODE 1 without penalty and gate, with the window, cap, sink and ring of PfBias.
+template <int HD, int BKV, int MODE>
 __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ q,
                                                               const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                                                               const int32_t* __restrict__ pos_dev, int M, int n_head, int n_kv, int max_seq,
                                                               float sqrt_hd, PfBias xb) {
+    constexpr bool BIAS = MODE == 1, WIN = MODE == 2, ROWS = MODE != 0;
     constexpr int CH = HD / 8;  // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t pf_smem[];
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(pf_smem);
@@ -567,13 +575,14 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     const uint32_t sV = sK + 2 * BKV * HD * 2;       // two V tiles
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) query tiles first
-    const int h = blockIdx.y, kvh = h / (n_head / n_kv), kv_dim = BIAS ? xb.kv_stride : n_kv * HD, q_dim = n_head * HD;
+    const int h = blockIdx.y, kvh = h / (n_head / n_kv), kv_dim = ROWS ? xb.kv_stride : n_kv * HD, q_dim = n_head * HD;
     const int pos0 = pos_dev[0];
-    if (BIAS) kc += (size_t)xb.slot[0] * xb.slot_stride, vc += (size_t)xb.slot[0] * xb.slot_stride;
+    if (ROWS) kc += (size_t)xb.slot[0] * xb.slot_stride, vc += (size_t)xb.slot[0] * xb.slot_stride;
     const float pen1 = BIAS ? bf16_bits_to_f32(xb.r1[h]) : 0.f, pen2 = BIAS ? bf16_bits_to_f32(xb.r2[h]) : 0.f;
     const int q0 = qt * kPfQ;
     const int kv_len = pos0 + min(M, q0 + kPfQ);  // rows visible to the last query row of this tile
     const int ntiles = (kv_len + BKV - 1) / BKV;
+    const int kt0 = WIN ? max(0, pos0 + q0 - xb.window + 1) / BKV : 0;  // the first tile that the tile's first query still sees
     auto sw = [](int row, int c) { return (uint32_t)((row * CH + (c ^ (row & 7))) * 16); };
 
     // ---- Q tile + first K / V tile ----
@@ -585,12 +594,13 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     auto load_kv = [&](int kt, int buf) {
         for (int i = tid; i < BKV * CH; i += 128) {
             const int r = i / CH, c = i % CH;
-            const int t = min(kt * BKV + r, max_seq - 1);  // rows past kv_len are masked below; keep the address inside the cache
+            // rows past kv_len are masked below; keep the address inside the cache (WIN: any row of the ring will do for those)
+            const int t = WIN ? (kt * BKV + r) % xb.ring : min(kt * BKV + r, max_seq - 1);
             cp16(sK + buf * (BKV * HD * 2) + sw(r, c), kc + (size_t)t * kv_dim + (size_t)kvh * HD + c * 8, true);
             cp16(sV + buf * (BKV * HD * 2) + sw(r, c), vc + (size_t)t * kv_dim + (size_t)kvh * HD + c * 8, true);
         }
     };
-    load_kv(0, 0);
+    load_kv(kt0, kt0 & 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     uint32_t qa[HD / 16][4];
@@ -600,15 +610,16 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     const int p_lo = pos0 + q0 + warp * 16 + g, p_hi = p_lo + 8;  // positions of this thread's two query rows
     // softmax((q.k)/sqrt(hd)) = 2^((q.k - max) * log2(e)/sqrt(hd)) / sum ; BIAS: the scores are brought to the log2 domain where the penalty joins
-    const float SC = BIAS ? 1.f : 1.4426950408889634f / sqrt_hd, SCB = xb.scale * 1.4426950408889634f;
+    const float SC = ROWS ? 1.f : 1.4426950408889634f / sqrt_hd, SCB = xb.scale * 1.4426950408889634f;
+    const float cap2 = (WIN && xb.softcap > 0.f) ? 2.f * 1.4426950408889634f / xb.softcap : 0.f, capL = xb.softcap * 1.4426950408889634f;
 
-    for (int kt = 0; kt < ntiles; kt++) {
+    for (int kt = kt0; kt < ntiles; kt++) {
         const int buf = kt & 1;
         if (kt + 1 < ntiles) load_kv(kt + 1, buf ^ 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
-        if (kt == 0) {
+        if (kt == kt0) {
 #pragma unroll
             for (int kc_ = 0; kc_ < HD / 16; kc_++) ldsm_x4(qa[kc_], sQ + sw(warp * 16 + (lane & 15), kc_ * 2 + (lane >> 4)));
         }
@@ -638,6 +649,12 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
                 if (BIAS) {
                     const int dist = ((e & 2) ? p_hi : p_lo) - (kt * BKV + j * 8 + 2 * t4 + (e & 1));
                     v = dist < 0 ? -INFINITY : fmaf(v, SCB, -pen1 * __log2f(fmaf(pen2, (float)dist, 1.f)));
+                } else if (WIN) {
+                    const int dist = ((e & 2) ? p_hi : p_lo) - (kt * BKV + j * 8 + 2 * t4 + (e & 1));
+                    // cap * tanh(s / cap) = cap * (1 - 2 / (e^{2 s / cap} + 1)), brought to the log2 domain
+                    if (cap2 > 0.f) v = capL * (1.f - __fdividef(2.f, exp2f(v * xb.scale * cap2) + 1.f));
+                    else v *= SCB;
+                    if (dist < 0 || dist >= xb.window) v = -INFINITY;
                 } else if (diag) {
                     const int tcol = kt * BKV + j * 8 + 2 * t4 + (e & 1);
                     if (tcol > ((e & 2) ? p_hi : p_lo)) v = -INFINITY;
@@ -654,7 +671,7 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
         const float c_lo = exp2f((m_lo - base_lo) * SC), c_hi = exp2f((m_hi - base_hi) * SC);
         m_lo = mn_lo, m_hi = mn_hi;
         float rs_lo = 0.f, rs_hi = 0.f;
-        uint32_t pa[BKV / 16][4], pb[BIAS ? BKV / 16 : 1][4];
+        uint32_t pa[BKV / 16][4], pb[ROWS ? BKV / 16 : 1][4];
 #pragma unroll
         for (int j = 0; j < BKV / 8; j++) {
             const float p0 = exp2f((sc[j][0] - base_lo) * SC), p1 = exp2f((sc[j][1] - base_lo) * SC);
@@ -663,7 +680,7 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
             const uint32_t w01 = pack_bf16x2(p0, p1), w23 = pack_bf16x2(p2, p3);
             pa[j >> 1][(j & 1) * 2 + 0] = w01;  // A fragment of P for the 16 tokens of n-tiles (2i, 2i+1)
             pa[j >> 1][(j & 1) * 2 + 1] = w23;
-            if (BIAS) {  // what the rounding dropped, as a second bf16 operand
+            if (ROWS) {  // what the rounding dropped, as a second bf16 operand
                 pb[j >> 1][(j & 1) * 2 + 0] = pack_bf16x2(p0 - bf16lo(w01), p1 - bf16hi(w01));
                 pb[j >> 1][(j & 1) * 2 + 1] = pack_bf16x2(p2 - bf16lo(w23), p3 - bf16hi(w23));
             }
@@ -680,7 +697,7 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
                 ldsm_x4_t(b, vb + sw(kc_ * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 2 + (lane >> 4)));
                 mma_bf16(o[2 * jp], pa[kc_], b[0], b[1]);
                 mma_bf16(o[2 * jp + 1], pa[kc_], b[2], b[3]);
-                if (BIAS) {
+                if (ROWS) {
                     mma_bf16(o[2 * jp], pb[kc_], b[0], b[1]);
                     mma_bf16(o[2 * jp + 1], pb[kc_], b[2], b[3]);
                 }
@@ -691,6 +708,14 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     // ---- normalise and store ----
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1), l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1), l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (WIN && xb.sink) {  // the sink counts once in the denominator and carries no value
+        const float s2 = bf16_bits_to_f32(xb.sink[h]) * 1.4426950408889634f;
+        const float n_lo = fmaxf(m_lo, s2), n_hi = fmaxf(m_hi, s2);
+        const float c_lo = exp2f(m_lo - n_lo), c_hi = exp2f(m_hi - n_hi);
+        l_lo = l_lo * c_lo + exp2f(s2 - n_lo), l_hi = l_hi * c_hi + exp2f(s2 - n_hi);
+#pragma unroll
+        for (int j = 0; j < HD / 8; j++) o[j][0] *= c_lo, o[j][1] *= c_lo, o[j][2] *= c_hi, o[j][3] *= c_hi;
+    }
     const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
     const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8;
 #pragma unroll
@@ -1058,6 +1083,41 @@ extern "C" int kf_attn_bias_prefill(kf_ctx* ctx, void* out, const void* q_bf16, 
         }
         kf_attn_prefill_kernel<64, KF_PF_BKV, true><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv,
                                                                                     max_seq, 1.f, xb);
+    }
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// The same panel attention over a sliding window of a ring cache (kf_attn_window of attn_window.cu on the tensor cores): q_bf16
+// [M][n_head * hd] normed and rotated; cache rows [slot][ring][n_kv * hd keys | n_kv * hd values] (bf16), position t in row t % ring;
+// out [M][n_head * hd] bf16.  window <= 0: all positions; softcap <= 0: scores are not capped; sink: bf16 [n_head] or NULL.
+extern "C" int kf_attn_window_prefill(kf_ctx* ctx, void* out, const void* q_bf16, const void* cache, size_t slot_stride, int ring, const void* sink_bf16,
+                                      const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale, float softcap,
+                                      int window) {
+    if (!ctx || !out || !q_bf16 || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, (hd == 128 || hd == 64) && n_head % n_kv == 0 && M >= 1 && ring >= 1 && (window <= 0 || ring >= window), "head size 64/128, GQA, ring");
+    const size_t smem = (size_t)(kPfQ + 4 * KF_PF_BKV) * hd * 2;
+    dim3 grid((M + kPfQ - 1) / kPfQ, n_head);
+    PfBias xb = {nullptr, nullptr, nullptr, 0, slot_dev, slot_stride, 2 * n_kv * hd, scale, ring, window > 0 ? window : 0x7fffffff, softcap,
+                 (const uint16_t*)sink_bf16};
+    const uint16_t* kc = (const uint16_t*)cache;
+    const uint16_t* vc = kc + (size_t)n_kv * hd;
+    if (hd == 128) {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<128, KF_PF_BKV, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<128, KF_PF_BKV, 2><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv, ring,
+                                                                                  1.f, xb);
+    } else {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<64, KF_PF_BKV, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<64, KF_PF_BKV, 2><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv, ring,
+                                                                                 1.f, xb);
     }
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;

@@ -29,6 +29,7 @@ __device__ __forceinline__ float ldc<float>(const float* p) { return *p; }
 
 struct PrepArgs {
     float* x;  // [M][ldx]: q (nq) | k (nk) | v (nv), consecutive
+    uint16_t* qb;  // optional bf16 copy of the finished q, [M][nq] (what the tensor-core panel kernel reads)
     int ldx, nq, nk, nv, hd;
     const uint16_t *qw, *kw;  // bf16 [nq], [nk] or NULL (that row is not normed)
     float eps, amp;
@@ -57,11 +58,14 @@ __global__ void __launch_bounds__(256) kf_qk_prepare_kernel(PrepArgs a) {
         if (i < a.nq) q2 = fmaf(v, v, q2);
         else k2 = fmaf(v, v, k2);
     }
-    // the angle is formed in double (pos * f_i exactly rounded once), its cosine and sine there too: at least what 32-bit asks
+    // the angle pos * f_i is formed and brought into [-pi, pi] in double (a few double operations), its cosine and sine in float: the
+    // reduced angle is exact to 2e-7, which is more than 32-bit angles keep at positions in the thousands
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos((double)p * a.inv_freq[i], &s, &c);
-        sc[i] = (float)c * a.amp, ss[i] = (float)s * a.amp;
+        const double ang = (double)p * a.inv_freq[i];
+        const float r = (float)(ang - 6.283185307179586 * rint(ang * 0.15915494309189535));
+        float s, c;
+        sincosf(r, &s, &c);
+        sc[i] = c * a.amp, ss[i] = s * a.amp;
     }
     q2 = block_sum(q2, red);
     k2 = block_sum(k2, red);
@@ -88,8 +92,10 @@ __global__ void __launch_bounds__(256) kf_qk_prepare_kernel(PrepArgs a) {
             const float o = sx[partner];
             v = first ? v * sc[f] - o * ss[f] : v * sc[f] + o * ss[f];
         }
-        if (i < a.nq) row[i] = v;
-        else if (sizeof(TC) == 2) ((uint16_t*)crow)[i - a.nq] = f32_to_bf16_bits(v);
+        if (i < a.nq) {
+            row[i] = v;
+            if (a.qb) a.qb[(size_t)m * a.nq + i] = f32_to_bf16_bits(v);
+        } else if (sizeof(TC) == 2) ((uint16_t*)crow)[i - a.nq] = f32_to_bf16_bits(v);
         else ((float*)crow)[i - a.nq] = v;
     }
     for (int i = threadIdx.x; i < a.nv; i += blockDim.x) {
@@ -243,10 +249,10 @@ __global__ void kf_attn_window_merge_kernel(WinArgs a) {
 // x[m] = [q (nq) | k (nk) | v (nv)] floats at row stride ldx.  q and k: RMS norm over the whole row part (weights bf16 [nq] / [nk]; NULL:
 // none), then the rotation of the first rot_dims entries of each head of size head_dim by pos[m] * inv_freq[i] with cos and sin times amp
 // (layout 0: pairs (2i, 2i+1); 1: pairs (i, i + rot_dims/2); rot_dims 0: none).  q is rewritten in place; k | v become row pos[m] % ring of
-// the slot's cache [slot][ring][nk + nv] in the cache's type.
+// the slot's cache [slot][ring][nk + nv] in the cache's type.  q_bf16_out (optional): a bf16 copy of the finished q, [M][nq].
 extern "C" int kf_qk_prepare(kf_ctx* ctx, float* x, int ldx, int nq, int nk, int nv, int head_dim, const void* q_norm_bf16, const void* k_norm_bf16, float eps,
                              int rot_dims, const double* inv_freq_dev, float amp, int layout, void* cache, int cache_f32, size_t slot_stride, int ring,
-                             const int32_t* pos_dev, const int32_t* slot_dev, int M) {
+                             void* q_bf16_out, const int32_t* pos_dev, const int32_t* slot_dev, int M) {
     if (!ctx || !x || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && nq >= 1 && nk >= 1 && nv >= 1 && head_dim >= 1 && nq % head_dim == 0 && nk % head_dim == 0 && ring >= 1, "shape");
     KF_REQUIRE(ctx, rot_dims >= 0 && rot_dims <= head_dim && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq_dev) && (layout == 0 || layout == 1), "rotation");
@@ -254,7 +260,7 @@ extern "C" int kf_qk_prepare(kf_ctx* ctx, float* x, int ldx, int nq, int nk, int
     PrepArgs a = {};
     a.x = x, a.ldx = ldx, a.nq = nq, a.nk = nk, a.nv = nv, a.hd = head_dim, a.qw = (const uint16_t*)q_norm_bf16, a.kw = (const uint16_t*)k_norm_bf16;
     a.eps = eps, a.amp = amp, a.rot_dims = rot_dims, a.layout = layout, a.inv_freq = inv_freq_dev, a.cache = cache, a.slot_stride = slot_stride, a.ring = ring;
-    a.pos = pos_dev, a.slot = slot_dev;
+    a.pos = pos_dev, a.slot = slot_dev, a.qb = (uint16_t*)q_bf16_out;
     const size_t smem = (size_t)(nq + nk + rot_dims) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "query + key row");
     if (cache_f32) kf_qk_prepare_kernel<float><<<M, 256, smem, ctx->stream>>>(a);

@@ -58,6 +58,28 @@ __global__ void kf_conv_tail_kernel(float* __restrict__ tail, size_t tail_stride
     }
 }
 
+// One token per sequence (decoding): the convolution and the advance of the tail in ONE launch.  A thread owns a channel of a sequence: it
+// reads the channel's stored inputs, forms the output with the same sum as kf_conv_silu_kernel, then shifts the tail by one.
+__global__ void kf_conv_step_kernel(float* __restrict__ out, const float* __restrict__ u, int ldu, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
+                                    float* __restrict__ tail, size_t tail_stride, const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int C, int K,
+                                    int act) {
+    const int m = blockIdx.x, p = pos[m];
+    float* tl = tail + (size_t)slot[m] * tail_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        const float cur = u[(size_t)m * ldu + c];
+        float s = b ? bf16_bits_to_f32(b[c]) : 0.f;
+        for (int j = 0; j < K; j++) {
+            const int back = K - 1 - j;
+            if (p - back < 0) continue;  // before the sequence started
+            const float v = back == 0 ? cur : tl[(size_t)(K - 1 - back) * C + c];
+            s = fmaf(bf16_bits_to_f32(w[(size_t)c * K + j]), v, s);
+        }
+        out[(size_t)m * C + c] = act ? s * sigmoid_f(s) : s;
+        for (int i = 0; i + 1 < K - 1; i++) tl[(size_t)i * C + c] = (p - (K - 2 - i) >= 0) ? tl[(size_t)(i + 1) * C + c] : 0.f;
+        if (K > 1) tl[(size_t)(K - 2) * C + c] = cur;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------ selective scan
 // grid (heads, sequences, p-chunks).  Thread (p, r) keeps NPT consecutive state rows n of column p in registers; the R threads of a
 // column are adjacent lanes and reduce y with shuffles.  Tokens are staged through shared memory TB at a time.
@@ -522,6 +544,12 @@ extern "C" int kf_conv1d(kf_ctx* ctx, float* xbc_out, const float* u, int ldu, i
                          size_t tail_stride, const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int C, int K, int act) {
     if (!ctx || !xbc_out || !u || !w_bf16 || !tail || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && C >= 1 && K >= 1 && tail_stride >= (size_t)(K - 1) * C, "shape");
+    if (T == 1) {  // decoding: output and tail in one launch
+        kf_conv_step_kernel<<<dim3(nseq, (C + 255) / 256), 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail,
+                                                                                tail_stride, pos_dev, slot_dev, C, K, act);
+        KF_LAUNCH_CHECK(ctx);
+        return KF_OK;
+    }
     kf_conv_silu_kernel<<<dim3(nseq * T, (C + 255) / 256), 256, 0, ctx->stream>>>(xbc_out, u + c0, ldu, (const uint16_t*)w_bf16, (const uint16_t*)b_bf16, tail, tail_stride, pos_dev,
                                                            slot_dev, T, C, K, act);
     KF_LAUNCH_CHECK(ctx);

@@ -226,7 +226,7 @@ static int BuildSedotar(Fish& f) {
         KF_TRY(b.Buf((char**)&blk->cat.w, (size_t)blk->cat.rows * E * 2));
         KF_TRY(kf_memset(f.ctx, blk->cat.w, 0, (size_t)blk->cat.rows * E * 2));
         maxU = std::max<size_t>(maxU, blk->cat.rows);
-        maxV = std::max<size_t>(maxV, Cl), maxL = std::max<size_t>(maxL, Cr), maxY = std::max<size_t>(maxY, rv);
+        maxV = std::max<size_t>(maxV, Cl), maxL = std::max<size_t>(maxL, Cr), maxY = std::max<size_t>(maxY, std::max(rv, nq / 2 + 1));  // scan read-out; the bf16 query of the panel kernel
         maxA = std::max<size_t>(maxA, no), maxMid = std::max<size_t>(maxMid, rv);
         blk->left = std::move(a), blk->right = std::move(d);
         if (lc.mlp.present) {
@@ -307,10 +307,17 @@ int WindowAttention::cuInfer(int M, const float* u, int ldu, int off, float* out
     SeqStateCache::Layer& sl = f.states.layers[layer];
     // q | k | v through their short convolutions (no activation); whole-row norms, rotation; this step's keys and values join the ring
     KF_TRY(kf_conv1d(f.ctx, s.v, u, ldu, off, convs.w, nullptr, sl.tail + tail_off, sl.tail_stride, f.d_pos, f.d_slot, nseq, T, C, m.conv, 0));
+    // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, other sizes, 32-bit) to the general kernel
+    const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && m.dim == m.vdim && (m.dim == 64 || m.dim == 128);
+    const void* snk = sink ? sink->data : nullptr;
     KF_TRY(kf_qk_prepare(f.ctx, s.v, C, nq, nk, nv, m.dim, qn->data, kn->data, c.norm_rms_eps, m.rot_dims, inv_freq, amp, 0, sl.rows, ak, sl.row_stride, sl.ring,
-                         f.d_pos, f.d_slot, M));
-    KF_TRY(kf_attn_window(f.ctx, s.act, ak, no, s.v, C, sl.rows, ak, sl.row_stride, sl.ring, sink ? sink->data : nullptr, f.d_pos, f.d_slot, M, m.heads, m.kv_heads,
-                          m.dim, m.vdim, m.scale, m.softcap, m.window, f.attn_hint + 1));
+                         tile ? s.y : nullptr, f.d_pos, f.d_slot, M));
+    if (tile)
+        KF_TRY(kf_attn_window_prefill(f.ctx, s.act, s.y, sl.rows, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.scale, m.softcap,
+                                      m.window));
+    else
+        KF_TRY(kf_attn_window(f.ctx, s.act, ak, no, s.v, C, sl.rows, ak, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.vdim,
+                              m.scale, m.softcap, m.window, f.attn_hint + 1));
     return Lin(f, out, c.n_embd, o, s.act, no, M);
 }
 

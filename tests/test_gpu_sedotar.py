@@ -75,6 +75,13 @@ def run_cut(model, toks, cuts, slot=0):
     return np.concatenate(out)
 
 
+def edited(cfg, fn):
+    """a copy of cfg whose first layer's attention card went through fn"""
+    c = json.loads(json.dumps(cfg))
+    fn(c["layers"][0]["mixer"]["left"])
+    return c
+
+
 FULL = [layer(),
         layer(left(heads=2, kv_heads=2, dim=8, vdim=40, conv=1, window=5, softcap=0, rot_dims=8, scaling=False), right(heads=2, kv_heads=1, dim=40, vdim=6, conv=1),
               ff=0),
@@ -148,6 +155,23 @@ def test_wide_panels_and_tuned_matmul_widths(ctx, f32):
     m.close()
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_panel_attention_on_tensor_cores(ctx, hd):
+    """bf16, key size = value size = 64 / 128: panels of 16 tokens and more run the tile kernel (peaked softmax, a cap that bites, sinks near
+    the largest scores, a window of 75 whose far edge falls inside 64-row tiles, panels that start inside a tile, a ring of 75 + 63 rows
+    that turns twice); smaller portions and decoded tokens run the general kernel on the same ring rows"""
+    cfg = config([layer(left(heads=4, kv_heads=2, dim=hd, vdim=hd, window=75, softcap=8.0, rot_dims=hd // 2, base=1000.0), ff=0, left_scale=1.0, right_scale=0.2)],
+                 width=64, vocab=80)
+    W = weights(cfg, seed=16, q_gain=6.0, sink=4.0)
+    toks = tokens(300, cfg["vocab"], 17)
+    want = oracle(cfg, W, toks)
+    assert rel(oracle(edited(cfg, lambda a: a["mask"].update(size=74)), W, toks), want) > 2 * TOL[False]
+    assert rel(oracle(cfg, {k: v for k, v in W.items() if k != "l0.mix.left.sink"}, toks), want) > 2 * TOL[False]
+    m = build(ctx, cfg, W, False, max_seq=320)
+    assert close(run_cut(m, toks, [64, 17, 3, 64, 30, 2, 16, 40, 64]), want, False)
+    m.close()
+
+
 def test_portions_of_many_sizes(ctx):
     cfg = config(FULL)
     W = weights(cfg, seed=6)
@@ -202,12 +226,6 @@ def test_batched_decode_of_unequal_requests(ctx):
 
 
 # ------------------------------------------------------------------------------------------------------------ shaped weights
-def edited(cfg, fn):
-    c = json.loads(json.dumps(cfg))
-    fn(c["layers"][0]["mixer"]["left"])
-    return c
-
-
 @pytest.mark.parametrize("f32", [True, False])
 def test_window_edges_cap_and_sink(ctx, f32):
     """a peaked softmax (query norm weights x 12) over a window of 23 positions, sinks near the largest scores, a cap that bites: the key that

@@ -1,7 +1,7 @@
 """One prompt in panels and a few decoded tokens of a bench model of koifish_b200/bench_arch.py: the workload for launch lists and
 single-kernel captures under ncu (few launches, nothing timed here).
 
-    python tools/arch_prompt_run.py [--size m] [--prompt 2048] [--panel 512] [--decode 3]
+    python tools/arch_prompt_run.py [--arch kivorax|kivorax_dense|sedotar] [--size m] [--prompt 2048] [--panel 512] [--decode 3]
 """
 import argparse
 import os
@@ -14,6 +14,7 @@ import koifish_b200 as kf  # noqa: E402
 from koifish_b200 import bench_arch as B  # noqa: E402
 
 ap = argparse.ArgumentParser()
+ap.add_argument("--arch", default="kivorax", choices=["kivorax", "kivorax_dense", "sedotar"])
 ap.add_argument("--size", default="m")
 ap.add_argument("--prompt", type=int, default=2048)
 ap.add_argument("--panel", type=int, default=512)
@@ -21,11 +22,12 @@ ap.add_argument("--decode", type=int, default=3)
 args = ap.parse_args()
 p = B.PRESETS[args.size]
 ctx = kf.Context(0)
-cfg = B.kivorax_config(p)
+cfg = {"kivorax": B.kivorax_config, "kivorax_dense": B.kivorax_dense_config, "sedotar": B.sedotar_config}[args.arch](p)
 model = kf.Model(ctx, {"hf_config": cfg, "gpt": {"max_seq_len": args.prompt + 64, "max_batch": 1, "max_prefill": args.panel},
                        "init": {"sigma": 0.02, "norm_sigma": 0.02}})
 model.init_random()
-B.kivorax_fixups(model, cfg)
+if args.arch != "sedotar":
+    B.kivorax_fixups(model, cfg)
 print("launches before the prompt", ctx.launches)
 toks = ((np.arange(args.prompt) * 37 + 11) % p["vocab"]).astype(np.int32)
 for lo in range(0, args.prompt, args.panel):
