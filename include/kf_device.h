@@ -110,6 +110,8 @@ int kf_memset(kf_ctx* ctx, void* dev, int value, size_t bytes);
 int kf_h2d(kf_ctx* ctx, void* dev, const void* host, size_t bytes);  /* async on the stream (pinned host) or staged */
 int kf_d2h(kf_ctx* ctx, void* host, const void* dev, size_t bytes);  /* async on the stream; call kf_ctx_sync before reading */
 int kf_d2d(kf_ctx* ctx, void* dst_dev, const void* src_dev, size_t bytes);
+/* `rows` rows of width_bytes each, pitches in bytes (a matrix copied into a column range of a wider one) */
+int kf_d2d_2d(kf_ctx* ctx, void* dst_dev, size_t dst_pitch, const void* src_dev, size_t src_pitch, size_t width_bytes, size_t rows);
 int kf_host_alloc(size_t bytes, void** host_out); /* pinned */
 int kf_host_free(void* host);
 
@@ -343,8 +345,8 @@ int kf_attn_bias_panel(kf_ctx* ctx, void* out_bf16_dev, void* q_work_bf16_dev, c
  *      reference equivalents ---- */
 /* kf_group_rmsnorm_ex with w_add added to every weight in fp32 (1 for weights stored around zero) */
 int kf_group_rmsnorm_wadd(kf_ctx* ctx, void* out_dev, int out_kind, int ldo, float* res_dev, float mult, const float* x_dev, int ldx, const float* gate_dev,
-                          int ldg, const void* gate_bias_bf16_dev, int gate_kind, const void* w_bf16_dev, int w_shared, float w_add, const int32_t* row_idx_dev,
-                          int rows, int dim, int groups, float eps);
+                          int ldg, const void* gate_bias_bf16_dev, int gate_kind, const void* w_bf16_dev, int w_shared, float w_add, float out_mult,
+                          const int32_t* row_idx_dev, int rows, int dim, int groups, float eps);  /* out_mult: factor on rows written to out (out_kind 0 / 1) */
 /* res[rows][dim] += rmsnorm(sa * a + sb * b) * (w_add + w) over the whole row (b may be NULL); act_out (optional) = the new res in the activation type */
 int kf_postnorm_residual(kf_ctx* ctx, float* res_dev, void* act_out_dev, int act_f32, const float* a_dev, int lda, float sa, const float* b_dev, int ldb, float sb,
                          const void* w_bf16_dev, float w_add, int rows, int dim, float eps);
@@ -363,11 +365,11 @@ int kf_qk_prepare(kf_ctx* ctx, float* x_dev, int ldx, int nq, int nk, int nv, in
  * (<= 0: not capped), a per-head sink term in the softmax denominator (bf16 [H] or NULL) */
 int kf_attn_window(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const void* cache_dev, int cache_f32, size_t slot_stride,
                    int ring, const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
-                   float softcap, int window, int max_keys_hint);
+                   float softcap, int window, int max_keys_hint, float out_scale /* factor on the result before it is written */);
 /* the same attention for a panel of M consecutive tokens of one slot on the tensor cores (bf16 ring cache, dk == dv in {64, 128}; attention.cu) */
-int kf_attn_window_prefill(kf_ctx* ctx, void* out_bf16_dev, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, int ring,
+int kf_attn_window_prefill(kf_ctx* ctx, void* out_bf16_dev, int ldo, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, int ring,
                            const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale,
-                           float softcap, int window);
+                           float softcap, int window, float out_scale);
 
 #ifdef __cplusplus
 }

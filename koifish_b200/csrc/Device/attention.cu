@@ -559,6 +559,8 @@ struct PfBias {
     int ring, window;
     float softcap;
     const uint16_t* sink;
+    int out_ld;       // MODE 2: elements between the output rows of consecutive tokens
+    float out_scale;  // MODE 2: factor on the result before it is rounded
 };
 // MODE 0: Qwen3's plain causal attention over separate K and V caches.  MODE 1: see above.  MODE 2: the side-by-side rows and hi + lo
 // softmax weights of MODE 1 without penalty and gate, with the window, cap, sink and ring of PfBias.
@@ -716,8 +718,8 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
 #pragma unroll
         for (int j = 0; j < HD / 8; j++) o[j][0] *= c_lo, o[j][1] *= c_lo, o[j][2] *= c_hi, o[j][3] *= c_hi;
     }
-    const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
-    const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8;
+    const float i_lo = (WIN ? xb.out_scale : 1.f) / l_lo, i_hi = (WIN ? xb.out_scale : 1.f) / l_hi;
+    const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8, o_dim = WIN ? xb.out_ld : q_dim;
 #pragma unroll
     for (int j = 0; j < HD / 8; j++) {
         const int d = j * 8 + 2 * t4;
@@ -732,8 +734,8 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
                 g2 = 1.f / (1.f + expf(-z.x)), g3 = 1.f / (1.f + expf(-z.y));
             }
         }
-        if (r_lo < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][0] * i_lo * g0, o[j][1] * i_lo * g1);
-        if (r_hi < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * q_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][2] * i_hi * g2, o[j][3] * i_hi * g3);
+        if (r_lo < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * o_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][0] * i_lo * g0, o[j][1] * i_lo * g1);
+        if (r_hi < M) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * o_dim + (size_t)h * HD + d) = pack_bf16x2(o[j][2] * i_hi * g2, o[j][3] * i_hi * g3);
     }
 }
 
@@ -1090,16 +1092,18 @@ extern "C" int kf_attn_bias_prefill(kf_ctx* ctx, void* out, const void* q_bf16, 
 
 // The same panel attention over a sliding window of a ring cache (kf_attn_window of attn_window.cu on the tensor cores): q_bf16
 // [M][n_head * hd] normed and rotated; cache rows [slot][ring][n_kv * hd keys | n_kv * hd values] (bf16), position t in row t % ring;
-// out [M][n_head * hd] bf16.  window <= 0: all positions; softcap <= 0: scores are not capped; sink: bf16 [n_head] or NULL.
-extern "C" int kf_attn_window_prefill(kf_ctx* ctx, void* out, const void* q_bf16, const void* cache, size_t slot_stride, int ring, const void* sink_bf16,
+// out [M][ldo] bf16 (n_head * hd entries per row, ldo even), times out_scale.  window <= 0: all positions; softcap <= 0: scores are not
+// capped; sink: bf16 [n_head] or NULL.
+extern "C" int kf_attn_window_prefill(kf_ctx* ctx, void* out, int ldo, const void* q_bf16, const void* cache, size_t slot_stride, int ring, const void* sink_bf16,
                                       const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale, float softcap,
-                                      int window) {
+                                      int window, float out_scale) {
     if (!ctx || !out || !q_bf16 || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, (hd == 128 || hd == 64) && n_head % n_kv == 0 && M >= 1 && ring >= 1 && (window <= 0 || ring >= window), "head size 64/128, GQA, ring");
+    KF_REQUIRE(ctx, (hd == 128 || hd == 64) && n_head % n_kv == 0 && M >= 1 && ring >= 1 && (window <= 0 || ring >= window) && ldo >= n_head * hd && ldo % 2 == 0,
+               "head size 64/128, GQA, ring");
     const size_t smem = (size_t)(kPfQ + 4 * KF_PF_BKV) * hd * 2;
     dim3 grid((M + kPfQ - 1) / kPfQ, n_head);
     PfBias xb = {nullptr, nullptr, nullptr, 0, slot_dev, slot_stride, 2 * n_kv * hd, scale, ring, window > 0 ? window : 0x7fffffff, softcap,
-                 (const uint16_t*)sink_bf16};
+                 (const uint16_t*)sink_bf16, ldo, out_scale};
     const uint16_t* kc = (const uint16_t*)cache;
     const uint16_t* vc = kc + (size_t)n_kv * hd;
     if (hd == 128) {

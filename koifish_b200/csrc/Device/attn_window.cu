@@ -116,12 +116,13 @@ struct WinArgs {
     const uint16_t* sink;  // bf16 [H] or NULL
     const int32_t *pos, *slot;
     int H, G, dk, dv;
-    float scale, softcap;
+    float scale, softcap, out_scale;
     int nsplit;  // the keys of a token are dealt to nsplit CTAs (blockIdx.z); > 1: partial (max, sum, weighted values) go to ws
     float* ws;   // [M][H][nsplit][dv + 2]
 };
 
 __device__ __forceinline__ void win_store(const WinArgs& a, int m, int h, int d, float o) {
+    o *= a.out_scale;
     if (a.out_f32) ((float*)a.out)[(size_t)m * a.ldo + h * a.dv + d] = o;
     else ((uint16_t*)a.out)[(size_t)m * a.ldo + h * a.dv + d] = f32_to_bf16_bits(o);
 }
@@ -272,16 +273,16 @@ extern "C" int kf_qk_prepare(kf_ctx* ctx, float* x, int ldx, int nq, int nk, int
 // out [M][ldo] (heads x dv, activation type) = attention of token m over the rows of positions max(0, pos[m] - window + 1) .. pos[m] of its
 // slot's ring (its own row appended before).  window <= 0: every position from 0; softcap <= 0: scores are not capped; sink: bf16 [H] or
 // NULL.  ring must cover the window (and, for window <= 0, every position).  max_keys_hint: an upper bound of the keys a token sees (sizes
-// the split of the keys over CTAs; the result does not depend on it beyond rounding).
+// the split of the keys over CTAs; the result does not depend on it beyond rounding).  out_scale multiplies the result before it is rounded.
 extern "C" int kf_attn_window(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* q, int ldq, const void* cache, int cache_f32, size_t slot_stride,
                               int ring, const void* sink_bf16, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
-                              float softcap, int window, int max_keys_hint) {
+                              float softcap, int window, int max_keys_hint, float out_scale) {
     if (!ctx || !out || !q || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dv <= 512 && ring >= 1 && (window <= 0 || ring >= window),
                "value size <= 512, kv heads divide heads, the ring covers the window");
     WinArgs a = {};
     a.out = out, a.ldo = ldo, a.out_f32 = out_f32, a.q = q, a.ldq = ldq, a.cache = cache, a.slot_stride = slot_stride, a.ring = ring, a.window = window;
-    a.sink = (const uint16_t*)sink_bf16, a.pos = pos_dev, a.slot = slot_dev, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.scale = scale, a.softcap = softcap;
+    a.sink = (const uint16_t*)sink_bf16, a.pos = pos_dev, a.slot = slot_dev, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
     const size_t smem = (size_t)(dk + AW * dv + AW * 2) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "key size");
     if (window > 0) max_keys_hint = std::min(max_keys_hint, window);

@@ -301,6 +301,12 @@ extern "C" int kf_d2d(kf_ctx* ctx, void* dst, const void* src, size_t bytes) {
     KF_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return KF_OK;
 }
+extern "C" int kf_d2d_2d(kf_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows) {
+    if (!ctx)
+        return KF_ERR_BAD_ARG;
+    KF_CUDA(ctx, cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, ctx->stream));
+    return KF_OK;
+}
 extern "C" int kf_host_alloc(size_t bytes, void** out) {
     if (!out)
         return KF_ERR_BAD_ARG;

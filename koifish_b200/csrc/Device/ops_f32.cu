@@ -75,7 +75,7 @@ template <int GATE, bool ACC, typename TO>
 __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out, int ldo, float* __restrict__ res, const float* __restrict__ x, int ldx,
                                                             const float* __restrict__ gate, int ldg, const uint16_t* __restrict__ gate_bias,
                                                             const uint16_t* __restrict__ w, const int32_t* __restrict__ row_idx, int dim, int groups,
-                                                            float eps, float mult, int w_shared, float w_add) {
+                                                            float eps, float mult, int w_shared, float w_add, float out_mult) {
     __shared__ float red[32];
     const int r = blockIdx.x, grp = blockIdx.y, gs = dim / groups;
     const int src = row_idx ? row_idx[r] : r;
@@ -108,9 +108,9 @@ __global__ void __launch_bounds__(256) kf_group_norm_kernel(TO* __restrict__ out
             float* p = res + (size_t)r * dim + grp * gs + i;
             *p       = *p + mult * o;
         } else if (sizeof(TO) == 2) {
-            ((uint16_t*)out)[(size_t)r * ldo + grp * gs + i] = f32_to_bf16_bits(o);
+            ((uint16_t*)out)[(size_t)r * ldo + grp * gs + i] = f32_to_bf16_bits(o * out_mult);
         } else {
-            ((float*)out)[(size_t)r * ldo + grp * gs + i] = o;
+            ((float*)out)[(size_t)r * ldo + grp * gs + i] = o * out_mult;
         }
     }
 }
@@ -359,17 +359,18 @@ extern "C" int kf_depth_mix(kf_ctx* ctx, float* x, float* hist, size_t hist_stri
 // gate_kind 0: none; 1: x * sigmoid(gate + gate_bias); 2: x * silu(gate).  out_kind 0: bf16 bits [rows][ldo]; 1: float [rows][ldo];
 // 2: res[rows][dim] += mult * result (out is ignored).  row_idx (device, optional): source row of each output row.
 // gate_kind 3 / 4: sigmoid(gate) / silu(gate) multiply the normed result; w_shared: the weight has dim / groups entries, used by every group.
-// w_add: added to every weight in fp32 (1 for weights stored around zero, 0 for plain weights).
+// w_add: added to every weight in fp32 (1 for weights stored around zero, 0 for plain weights).  out_mult: factor on the rows written to
+// out (out_kind 0 / 1), applied in fp32 before the rounding.
 extern "C" int kf_group_rmsnorm_wadd(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
-                                     const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, float w_add, const int32_t* row_idx, int rows,
-                                     int dim, int groups, float eps) {
+                                     const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, float w_add, float out_mult,
+                                     const int32_t* row_idx, int rows, int dim, int groups, float eps) {
     if (!ctx || !x || !w_bf16) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, rows >= 1 && dim >= 1 && groups >= 1 && dim % groups == 0, "groups must divide dim");
     KF_REQUIRE(ctx, gate_kind >= 0 && gate_kind <= 4 && (gate_kind == 0 || gate) && out_kind >= 0 && out_kind <= 2 && (out_kind == 2 ? res != nullptr : out != nullptr),
                "gate / out kind");
     dim3 grid(rows, groups);
     const uint16_t *gb = (const uint16_t*)gate_bias_bf16, *w = (const uint16_t*)w_bf16;
-#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult, w_shared, w_add)
+#define KF_GN(G, A, T) kf_group_norm_kernel<G, A, T><<<grid, 256, 0, ctx->stream>>>((T*)out, ldo, res, x, ldx, gate, ldg, gb, w, row_idx, dim, groups, eps, mult, w_shared, w_add, out_mult)
     if (out_kind == 2) {
         if (gate_kind == 0) KF_GN(0, true, float);
         else if (gate_kind == 1) KF_GN(1, true, float);
@@ -396,8 +397,8 @@ extern "C" int kf_group_rmsnorm_wadd(kf_ctx* ctx, void* out, int out_kind, int l
 extern "C" int kf_group_rmsnorm_ex(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
                                    const void* gate_bias_bf16, int gate_kind, const void* w_bf16, int w_shared, const int32_t* row_idx, int rows, int dim,
                                    int groups, float eps) {
-    return kf_group_rmsnorm_wadd(ctx, out, out_kind, ldo, res, mult, x, ldx, gate, ldg, gate_bias_bf16, gate_kind, w_bf16, w_shared, 0.f, row_idx, rows, dim,
-                                 groups, eps);
+    return kf_group_rmsnorm_wadd(ctx, out, out_kind, ldo, res, mult, x, ldx, gate, ldg, gate_bias_bf16, gate_kind, w_bf16, w_shared, 0.f, 1.f, row_idx, rows,
+                                 dim, groups, eps);
 }
 extern "C" int kf_group_rmsnorm(kf_ctx* ctx, void* out, int out_kind, int ldo, float* res, float mult, const float* x, int ldx, const float* gate, int ldg,
                                 const void* gate_bias_bf16, int gate_kind, const void* w_bf16, const int32_t* row_idx, int rows, int dim, int groups,

@@ -166,7 +166,7 @@ static int BuildSedotar(Fish& f) {
     const size_t T = f.max_tokens;
     auto hs    = std::make_shared<HybridScratch>();
     f.hscratch = hs;
-    size_t maxU = 1, maxV = 1, maxY = 1, maxL = 1, maxA = 1, maxMid = 1, maxH1 = 1;
+    size_t maxU = 1, maxV = 1, maxY = 1, maxL = 1, maxA = 1, maxH1 = 1;
     f.states.layers.resize(L);
     f.states.max_seq = c.max_seq_len, f.states.f32 = f32;
     for (int i = 0; i < L; i++) {
@@ -227,7 +227,9 @@ static int BuildSedotar(Fish& f) {
         KF_TRY(kf_memset(f.ctx, blk->cat.w, 0, (size_t)blk->cat.rows * E * 2));
         maxU = std::max<size_t>(maxU, blk->cat.rows);
         maxV = std::max<size_t>(maxV, Cl), maxL = std::max<size_t>(maxL, Cr), maxY = std::max<size_t>(maxY, std::max(rv, nq / 2 + 1));  // scan read-out; the bf16 query of the panel kernel
-        maxA = std::max<size_t>(maxA, no), maxMid = std::max<size_t>(maxMid, rv);
+        blk->out.Plan({a->o, d->o});
+        KF_TRY(b.Buf((char**)&blk->out.w, (size_t)E * blk->out.cols * 2));
+        maxA = std::max<size_t>(maxA, blk->out.cols);
         blk->left = std::move(a), blk->right = std::move(d);
         if (lc.mlp.present) {
             auto e = std::make_unique<GatedFF>();
@@ -248,13 +250,11 @@ static int BuildSedotar(Fish& f) {
     KF_TRY(kf_malloc(f.ctx, T * E * 4, &f.x));
     KF_TRY(b.Buf((char**)&hs->hact, T * E * asz));
     KF_TRY(b.Buf(&hs->sub, T * E * 4));
-    KF_TRY(b.Buf(&hs->shared, T * E * 4));
     KF_TRY(b.Buf(&hs->u, T * maxU * 4));
     KF_TRY(b.Buf(&hs->v, T * maxV * 4));
     KF_TRY(b.Buf(&hs->lat, T * maxL * 4));
     KF_TRY(b.Buf(&hs->y, T * maxY * 4));
     KF_TRY(b.Buf((char**)&hs->act, T * maxA * asz));
-    KF_TRY(b.Buf((char**)&hs->mid, T * maxMid * asz));
     KF_TRY(b.Buf((char**)&hs->h1, T * maxH1 * asz));
     KF_TRY(b.Buf((char**)&hs->head_in, (size_t)f.logit_rows * E * asz));
     KF_TRY(kf_malloc(f.ctx, (size_t)f.logit_rows * c.vocab * 2, &f.logits));
@@ -272,10 +272,22 @@ static int BuildSedotar(Fish& f) {
     return KF_OK;
 }
 
+void SummedLinear::Plan(const std::vector<hGTensor>& tensors) {
+    parts = tensors, off.clear(), cols = 0, rows = tensors[0]->ne[0];
+    for (auto& t : parts) off.push_back(cols), cols += t->ne[1];
+}
+int SummedLinear::Fill(kf_ctx* ctx) const {
+    for (size_t i = 0; i < parts.size(); i++) {
+        int rc = kf_d2d_2d(ctx, (char*)w + (size_t)off[i] * 2, (size_t)cols * 2, parts[i]->data, (size_t)parts[i]->ne[1] * 2, (size_t)parts[i]->ne[1] * 2, (size_t)rows);
+        if (rc) return rc;
+    }
+    return KF_OK;
+}
 static int PrepareSedotar(Fish& f) {
     for (auto& n : f.blocks) {
         SedotarBlock* b = static_cast<SedotarBlock*>(n.get());
         int rc = b->cat.Fill(f.ctx);
+        if (!rc) rc = b->out.Fill(f.ctx);
         if (!rc) rc = b->left->convs.Fill(f.ctx);
         if (!rc) rc = b->right->convs.Fill(f.ctx);
         if (!rc && b->ff) rc = b->ff->cat.Fill(f.ctx);
@@ -295,33 +307,33 @@ static int LinStacked(Fish& f, float* y, const StackedLinear& s, const void* x, 
     return kf_linear_g(f.ctx, y, s.rows, &d, x, f.config.compute_f32 ? 1 : 0, s.cols, M);
 }
 
-int WindowAttention::cuInfer(int M, const float* u, int ldu, int off, float* out) {
+int WindowAttention::cuInfer(int M, const float* u, int ldu, int off, void* out, int ldo, float out_scale) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
     const MIXER_CARD& m = card;
     const MODEL_CARD& c = f.config;
     const int ak = c.compute_f32 ? 1 : 0;
-    const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, C = nq + nk + nv;
+    const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, C = nq + nk + nv;
     const int nseq = f.seq_mode ? M : 1, T = f.seq_mode ? 1 : M;
     SeqStateCache::Layer& sl = f.states.layers[layer];
     // q | k | v through their short convolutions (no activation); whole-row norms, rotation; this step's keys and values join the ring
     KF_TRY(kf_conv1d(f.ctx, s.v, u, ldu, off, convs.w, nullptr, sl.tail + tail_off, sl.tail_stride, f.d_pos, f.d_slot, nseq, T, C, m.conv, 0));
     // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, other sizes, 32-bit) to the general kernel
-    const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && m.dim == m.vdim && (m.dim == 64 || m.dim == 128);
+    const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && m.dim == m.vdim && (m.dim == 64 || m.dim == 128) && ldo % 2 == 0;
     const void* snk = sink ? sink->data : nullptr;
     KF_TRY(kf_qk_prepare(f.ctx, s.v, C, nq, nk, nv, m.dim, qn->data, kn->data, c.norm_rms_eps, m.rot_dims, inv_freq, amp, 0, sl.rows, ak, sl.row_stride, sl.ring,
                          tile ? s.y : nullptr, f.d_pos, f.d_slot, M));
     if (tile)
-        KF_TRY(kf_attn_window_prefill(f.ctx, s.act, s.y, sl.rows, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.scale, m.softcap,
-                                      m.window));
+        KF_TRY(kf_attn_window_prefill(f.ctx, out, ldo, s.y, sl.rows, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.scale,
+                                      m.softcap, m.window, out_scale));
     else
-        KF_TRY(kf_attn_window(f.ctx, s.act, ak, no, s.v, C, sl.rows, ak, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.vdim,
-                              m.scale, m.softcap, m.window, f.attn_hint + 1));
-    return Lin(f, out, c.n_embd, o, s.act, no, M);
+        KF_TRY(kf_attn_window(f.ctx, out, ak, ldo, s.v, C, sl.rows, ak, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.vdim,
+                              m.scale, m.softcap, m.window, f.attn_hint + 1, out_scale));
+    return KF_OK;
 }
 
-int ScalarDeltaMixer::cuInfer(int M, const float* u, int ldu, const int* off, float* out) {
+int ScalarDeltaMixer::cuInfer(int M, const float* u, int ldu, const int* off, void* out, int ldo, float out_scale) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
@@ -335,8 +347,9 @@ int ScalarDeltaMixer::cuInfer(int M, const float* u, int ldu, const int* off, fl
     KF_TRY(kf_gated_scan_ex(f.ctx, s.y, nv, s.lat, C, s.lat + nq, C, s.lat + 2 * nq, C, u + off[2], ldu, dt_bias->data, A_log->data, u + off[1], ldu, sl.state,
                             sl.state_stride, f.d_pos, f.d_slot, nseq, T, m.heads, m.kv_heads, m.dim, m.vdim, 1, 1, 1.f, 1, 1e-6f, 1.0f / std::sqrt((float)m.dim), 1));
     // per-head RMS norm of the read-out (weight shared by the heads) times silu(gate)
-    KF_TRY(kf_group_rmsnorm_ex(f.ctx, s.mid, ak, nv, nullptr, 0.f, s.y, nv, u + off[3], ldu, nullptr, 4, norm->data, 1, nullptr, M, nv, m.heads, c.norm_rms_eps));
-    return Lin(f, out, c.n_embd, o, s.mid, nv, M);
+    KF_TRY(kf_group_rmsnorm_wadd(f.ctx, out, ak, ldo, nullptr, 0.f, s.y, nv, u + off[3], ldu, nullptr, 4, norm->data, 1, 0.f, out_scale, nullptr, M, nv, m.heads,
+                                 c.norm_rms_eps));
+    return KF_OK;
 }
 
 int SedotarBlock::cuInfer(int M) {
@@ -349,11 +362,17 @@ int SedotarBlock::cuInfer(int M) {
     float* x = (float*)f.x;
     // hact holds x in the activation type (written by whoever updated x last).  One matmul for everything in the mixer that reads it.
     KF_TRY(LinStacked(f, s.u, cat, s.hact, M));
-    KF_TRY(left->cuInfer(M, s.u, cat.rows, off[0], s.sub));
+    // each branch leaves (its scale) x (its result) in its columns of `act`; one matmul over [W_o left | W_o right] then forms
+    // left_scale * W_l y_l + right_scale * W_r y_r
+    const size_t asz = ak ? 4 : 2;
+    KF_TRY(left->cuInfer(M, s.u, cat.rows, off[0], s.act, out.cols, m.left_scale));
     const int roff[4] = {off[3], off[6], off[7], off[8]};
-    KF_TRY(right->cuInfer(M, s.u, cat.rows, roff, s.shared));
-    // x += norm1(left_scale * left + right_scale * right); hact = the new x
-    KF_TRY(kf_postnorm_residual(f.ctx, x, s.hact, ak, s.sub, E, m.left_scale, s.shared, E, m.right_scale, norm1.w->data, 1.f, M, E, norm1.eps));
+    KF_TRY(right->cuInfer(M, s.u, cat.rows, roff, (char*)s.act + (size_t)out.off[1] * asz, out.cols, m.right_scale));
+    kf_tensor_desc dw = {};
+    dw.data_dev = out.w, dw.rows = out.rows, dw.cols = out.cols, dw.type = KF_T_BF16, dw.group = 128;
+    KF_TRY(kf_linear_g(f.ctx, s.sub, E, &dw, s.act, ak, out.cols, M));
+    // x += norm1(mixer); hact = the new x
+    KF_TRY(kf_postnorm_residual(f.ctx, x, s.hact, ak, s.sub, E, 1.f, nullptr, 0, 0.f, norm1.w->data, 1.f, M, E, norm1.eps));
     if (ff) {
         const int F = ff->card.ff;
         KF_TRY(LinStacked(f, s.u, ff->cat, s.hact, M));
@@ -375,8 +394,8 @@ static int ForwardSedotar(Fish& f, int M, bool want_logits) {
     for (auto& n : f.blocks) KF_TRY(static_cast<SedotarBlock*>(n.get())->cuInfer(M));
     if (want_logits && f.n_rows > 0) {
         const int R = f.n_rows;
-        KF_TRY(kf_group_rmsnorm_wadd(f.ctx, s.head_in, ak, E, nullptr, 0.f, (float*)f.x, E, nullptr, 0, nullptr, 0, f.cls.norm.w->data, 0, 1.f, f.d_sel, R, E, 1,
-                                     c.norm_rms_eps));
+        KF_TRY(kf_group_rmsnorm_wadd(f.ctx, s.head_in, ak, E, nullptr, 0.f, (float*)f.x, E, nullptr, 0, nullptr, 0, f.cls.norm.w->data, 0, 1.f, 1.f, f.d_sel, R,
+                                     E, 1, c.norm_rms_eps));
         KF_TRY(Lin(f, f.logits_f32, c.vocab, f.cls.proj.w, s.head_in, E, R));
         KF_TRY(kf_f32_to_bf16(f.ctx, f.logits, f.logits_f32, (size_t)R * c.vocab));
     }

@@ -26,8 +26,8 @@ struct WindowAttention : GeNeuron {
     double* inv_freq = nullptr;   // device [rot_dims / 2], stretched frequencies
     float amp = 1.f;              // multiplies cosine and sine
     size_t tail_off = 0;          // where this mixer's convolution inputs start inside the layer's tail region
-    // u: the stacked first projections, q | k | v at column off; the attended values go to scratch `act`, the projection to `out`
-    int cuInfer(int M, const float* u, int ldu, int off, float* out);
+    // u: the stacked first projections, q | k | v at column off; out_scale * (attended values) go to out [M][ldo] in the activation type
+    int cuInfer(int M, const float* u, int ldu, int off, void* out, int ldo, float out_scale);
 };
 struct ScalarDeltaMixer : GeNeuron {
     MIXER_CARD card;
@@ -35,17 +35,29 @@ struct ScalarDeltaMixer : GeNeuron {
     hGTensor q, k, v, qc, kc, vc, b, a, A_log, dt_bias, norm, g, o;
     StackedLinear convs;
     size_t tail_off = 0;
-    int cuInfer(int M, const float* u, int ldu, const int* off, float* out);  // off: q (k, v follow), b, a, g
+    // off: columns of q (k, v follow), b, a, g in u; out_scale * (gated, normed read-out) goes to out [M][ldo] in the activation type
+    int cuInfer(int M, const float* u, int ldu, const int* off, void* out, int ldo, float out_scale);
 };
 struct GatedFF : GeNeuron {  // down(act(gate x) * (up x)), act = relu
     MOE_CARD card;
     hGTensor gate, up, down;
     StackedLinear cat;  // gate | up
 };
+// Several weights whose results are ADDED, stacked column-wise into ONE matrix at load: y = [W_a | W_b] [x_a ; x_b] = W_a x_a + W_b x_b in
+// one launch; the producers write x_a and x_b side by side at off[i] of a row of `cols` entries.
+struct SummedLinear {
+    void* w = nullptr;  // device bf16 [rows][cols]
+    int rows = 0, cols = 0;
+    std::vector<hGTensor> parts;
+    std::vector<int> off;
+    void Plan(const std::vector<hGTensor>& tensors);
+    int Fill(kf_ctx* ctx) const;
+};
 struct SedotarBlock : GeNeuron {
     int layer = 0;
     GroupNorm norm1, norm2;
     StackedLinear cat;  // everything that reads x in the mixer: left q k v, right q k v b a g
+    SummedLinear out;   // left o | right o: the branch scales ride on the branches' outputs, so one matmul forms a_l W_l y_l + a_r W_r y_r
     std::vector<int> off;
     std::unique_ptr<WindowAttention> left;
     std::unique_ptr<ScalarDeltaMixer> right;
