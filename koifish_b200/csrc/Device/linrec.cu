@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
     float* sG = sQ + TB * dkp;       // [TB][dkp]
     float* sV = sG + TB * dkp;       // [TB][PB]
     float* sB = sV + TB * PB;        // [TB]
+    float* sKQ = sB + TB;            // [TB] k . q of the staged (normalised, scaled) rows: the delta rule's read-out needs it
     const int h = blockIdx.x, seq = blockIdx.y, p0 = blockIdx.z * PB;
     const int kh = h / (a.H / a.G);
     const int tid = threadIdx.x, pl = tid / R, r = tid - pl * R, p = p0 + pl;
@@ -119,9 +120,16 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
             }
             const float fq = a.unit_qk ? a.q_scale / sqrtf(sq + a.unit_eps) : a.q_scale;
             const float fk = a.unit_qk ? 1.f / sqrtf(sk + a.unit_eps) : 1.f;
+            float kq = 0.f;
             for (int n = lane; n < dk; n += 32) {
-                sQ[tt * dkp + ix(n)] *= fq;
-                if (a.unit_qk) sK[tt * dkp + ix(n)] *= fk;
+                const float qn = sQ[tt * dkp + ix(n)] * fq, kn = sK[tt * dkp + ix(n)] * fk;
+                sQ[tt * dkp + ix(n)] = qn;
+                if (a.unit_qk) sK[tt * dkp + ix(n)] = kn;
+                kq = fmaf(kn, qn, kq);
+            }
+            if (DELTA) {
+                kq = warp_sum(kq);
+                if (lane == 0) sKQ[tt] = kq;
             }
         }
         __syncthreads();
@@ -149,20 +157,27 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
             const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
             float w = vv;
             if (DELTA) {
-                float d[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: the dependent chain is 4 deep, not 16
+                // With D = diag(g) S the write is S' = D + k w^T, so the read-out S'^T q = D^T q + (k . q) w: both sums run over D in ONE pass
+                // (two independent chains, their cross-lane sums interleaved) instead of a second pass over S' that waits for w.
+                float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums each: the chains are 4 deep, not 16
 #pragma unroll
                 for (int i = 0; i < NPT; i++) {
                     S[i] *= gg[i];
                     d[i & 3] = fmaf(S[i], kk[i], d[i & 3]);
+                    e[i & 3] = fmaf(S[i], qq[i], e[i & 3]);
                 }
-                float dot = (d[0] + d[1]) + (d[2] + d[3]);
-                for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                float dot = (d[0] + d[1]) + (d[2] + d[3]), rd = (e[0] + e[1]) + (e[2] + e[3]);
+                for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o), rd += __shfl_xor_sync(0xffffffffu, rd, o);
                 w = sB[tt] * (vv - dot);
+#pragma unroll
+                for (int i = 0; i < NPT; i++) S[i] = fmaf(kk[i], w, S[i]);
+                if (live && r == 0) a.y[(size_t)(m0 + t0 + tt) * a.ldy + h * a.dv + p] = fmaf(sKQ[tt], w, rd);
+                continue;
             }
             float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < NPT; i++) {
-                S[i]     = DELTA ? fmaf(kk[i], w, S[i]) : fmaf(gg[i], S[i], kk[i] * w);
+                S[i]     = fmaf(gg[i], S[i], kk[i] * w);
                 c[i & 3] = fmaf(S[i], qq[i], c[i & 3]);
             }
             float acc = (c[0] + c[1]) + (c[2] + c[3]);
@@ -294,9 +309,9 @@ extern "C" int kf_gated_scan_ex(kf_ctx* ctx, float* y, int ldy, const float* q, 
     const int PB = std::max(1, std::min(dv, 256 / R));
     const int threads = std::max(32, ((PB * R + 31) / 32) * 32);
     const int dkp = ((dk + 15) / 16) * 20;
-    int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dkp + PB + 1));
+    int TB = (int)std::min<size_t>(32, (44 * 1024 / sizeof(float)) / (size_t)(3 * dkp + PB + 2));
     TB = std::max(1, std::min(TB, T));
-    const size_t smem = (size_t)(3 * TB * dkp + TB * PB + TB) * sizeof(float);
+    const size_t smem = (size_t)(3 * TB * dkp + TB * PB + 2 * TB) * sizeof(float);
     KF_REQUIRE(ctx, smem <= 48 * 1024, "staging area");
     a.R = R, a.PB = PB, a.TB = TB, a.dkp = dkp;
     const dim3 grid(H, nseq, (dv + PB - 1) / PB);
