@@ -126,6 +126,13 @@ SIGNATURES = {
     "kf_attn_bias": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _P, _I, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I]),
     "kf_attn_bias_prefill": (_I, [_P, _P, _P, _P, _SZ, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F]),
     "kf_attn_bias_panel": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I]),
+    "kf_gated_scan_ex": (_I, [_P, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _F, _F, _I]),
+    "kf_group_rmsnorm_wadd": (_I, [_P, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P, _I, _F, _F, _P, _I, _I, _I, _F]),
+    "kf_postnorm_residual": (_I, [_P, _P, _P, _I, _P, _I, _F, _P, _I, _F, _P, _F, _I, _I, _F]),
+    "kf_qk_prepare": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _P, _F, _I, _P, _I, _SZ, _I, _P, _P, _P, _I]),
+    "kf_attn_window": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _F]),
+    "kf_attn_window_prefill": (_I, [_P, _P, _I, _P, _P, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _F]),
+    "kf_d2d_2d": (_I, [_P, _P, _SZ, _P, _SZ, _SZ, _SZ]),
     "kf_nccl_unique_id": (_I, [_P]),
     "kf_ctx_init_nccl": (_I, [_P, _P, _I, _I]),
     "kf_allreduce_bf16": (_I, [_P, _P, _SZ]),

@@ -40,12 +40,12 @@ struct ScanArgs {
     float inv_tau, q_scale, unit_eps;
 };
 
-// grid (heads, sequences, column chunks).  Thread (pl, r) keeps the NPT consecutive rows n = r * NPT + i of state column p0 + pl in
+// grid (heads, sequences, column chunks).  Thread (pl, r) keeps the NPT (16 or 8) consecutive rows n = r * NPT + i of state column p0 + pl in
 // registers; the R lanes of a column are adjacent and reduce with shuffles.  TB tokens are staged in shared memory per pass: k, q
-// (normalised there), the decay (formed there), v, beta.  FULL (dk == R * NPT): a thread's slice of k, q and the decay is four 16-byte
+// (normalised there), the decay (formed there), v, beta.  FULL (dk == R * NPT): a thread's slice of k, q and the decay is NPT / 4 16-byte
 // shared loads each and nothing is bounds-checked; otherwise rows beyond dk read k = q = 0 and leave their (zero) state alone.
-constexpr int NPT = 16;
-template <bool DELTA, bool FULL>
+constexpr int NPT_MAX = 16;
+template <bool DELTA, bool FULL, int NPT>
 __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float sm[];
     // staged rows are padded by 4 floats after every 16: the R lanes of a column read slices 20 floats apart, which fall into different
@@ -295,13 +295,15 @@ extern "C" int kf_gated_scan_ex(kf_ctx* ctx, float* y, int ldy, const float* q, 
                              const int32_t* pos_dev, const int32_t* slot_dev, int nseq, int T, int H, int G, int dk, int dv, int delta, int decay_kind,
                              float tau, int unit_qk, float unit_eps, float q_scale, int decay_per_head) {
     if (!ctx || !y || !q || !k || !v || !z || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 32 * NPT, "key size <= 512, kv heads divide heads");
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && H >= 1 && G >= 1 && H % G == 0 && dk >= 1 && dv >= 1 && dk <= 32 * NPT_MAX, "key size <= 512, kv heads divide heads");
     KF_REQUIRE(ctx, (!delta || beta_logit) && (decay_kind == 0 ? tau > 0.f : A_log_bf16 != nullptr) && state_stride >= (size_t)H * dk * dv, "arguments");
     ScanArgs a = {};
     a.y = y, a.ldy = ldy, a.q = q, a.k = k, a.v = v, a.z = z, a.beta = beta_logit, a.ldq = ldq, a.ldk = ldk, a.ldv = ldv, a.ldz = ldz, a.ldb = ldb;
     a.zbias = (const uint16_t*)zbias_bf16, a.A_log = (const uint16_t*)A_log_bf16, a.state = state, a.state_stride = state_stride;
     a.pos = pos_dev, a.slot = slot_dev, a.T = T, a.H = H, a.G = G, a.dk = dk, a.dv = dv, a.delta = delta, a.decay_kind = decay_kind;
     a.unit_qk = unit_qk, a.inv_tau = decay_kind == 0 ? 1.f / tau : 0.f, a.q_scale = q_scale, a.unit_eps = unit_eps, a.z_head = decay_per_head ? 1 : 0;
+    // rows of a state column per lane: 16, or 8 for keys of up to 128 entries (a shorter dependent chain per token, twice the lanes per column)
+    const int NPT = (dk <= 128 && dk % 8 == 0 && dk >= 16) ? 8 : 16;
     int R = 1;
     while (R * NPT < dk) R <<= 1;
     // up to 256 threads per CTA: the per-token chain of a warp is latency-bound and as long whatever the grid, while the staging of a pass (and
@@ -316,13 +318,17 @@ extern "C" int kf_gated_scan_ex(kf_ctx* ctx, float* y, int ldy, const float* q, 
     a.R = R, a.PB = PB, a.TB = TB, a.dkp = dkp;
     const dim3 grid(H, nseq, (dv + PB - 1) / PB);
     const bool full = dk == R * NPT;
+#define KF_SCAN(D, F, N) kf_gated_scan_kernel<D, F, N><<<grid, threads, smem, ctx->stream>>>(a)
+#define KF_SCAN_N(D, F) (NPT == 8 ? KF_SCAN(D, F, 8) : KF_SCAN(D, F, 16))
     if (delta) {
-        if (full) kf_gated_scan_kernel<true, true><<<grid, threads, smem, ctx->stream>>>(a);
-        else kf_gated_scan_kernel<true, false><<<grid, threads, smem, ctx->stream>>>(a);
+        if (full) KF_SCAN_N(true, true);
+        else KF_SCAN_N(true, false);
     } else {
-        if (full) kf_gated_scan_kernel<false, true><<<grid, threads, smem, ctx->stream>>>(a);
-        else kf_gated_scan_kernel<false, false><<<grid, threads, smem, ctx->stream>>>(a);
+        if (full) KF_SCAN_N(false, true);
+        else KF_SCAN_N(false, false);
     }
+#undef KF_SCAN_N
+#undef KF_SCAN
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }

@@ -322,14 +322,16 @@ int WindowAttention::cuInfer(int M, const float* u, int ldu, int off, void* out,
     // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, other sizes, 32-bit) to the general kernel
     const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && m.dim == m.vdim && (m.dim == 64 || m.dim == 128) && ldo % 2 == 0;
     const void* snk = sink ? sink->data : nullptr;
+    // a window longer than the ring means the ring was cut to max_seq rows: every position is below it and none is ever masked
+    const int win = m.window <= sl.ring ? m.window : 0;
     KF_TRY(kf_qk_prepare(f.ctx, s.v, C, nq, nk, nv, m.dim, qn->data, kn->data, c.norm_rms_eps, m.rot_dims, inv_freq, amp, 0, sl.rows, ak, sl.row_stride, sl.ring,
                          tile ? s.y : nullptr, f.d_pos, f.d_slot, M));
     if (tile)
         KF_TRY(kf_attn_window_prefill(f.ctx, out, ldo, s.y, sl.rows, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.scale,
-                                      m.softcap, m.window, out_scale));
+                                      m.softcap, win, out_scale));
     else
         KF_TRY(kf_attn_window(f.ctx, out, ak, ldo, s.v, C, sl.rows, ak, sl.row_stride, sl.ring, snk, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.vdim,
-                              m.scale, m.softcap, m.window, f.attn_hint + 1, out_scale));
+                              m.scale, m.softcap, win, f.attn_hint + 1, out_scale));
     return KF_OK;
 }
 

@@ -99,12 +99,13 @@ FULL = [layer(),
     layer(left(heads=3, kv_heads=3, dim=8, vdim=8, conv=1, rot_dims=8), ff=0, right_scale=0.0),              # no grouping, one tap, every entry rotated
     layer(left(heads=1, kv_heads=1, dim=6, vdim=70, window=1, rot_dims=2, scaling=False), ff=0, right_scale=0.0),  # one head, a window of the token itself, wide values
     layer(left(window=0, softcap=0, rot_dims=0), ff=0, right_scale=0.0),                     # all keys, no cap, no rotation: plain attention with a sink
+    layer(left(window=1000), ff=0, right_scale=0.0),                                         # a window longer than the model's context
     layer(left(scaling={"factor": 16.0, "original": 20, "fast": 2.0, "slow": 0.5}, rot_dims=12, base=200.0), ff=0, right_scale=0.0),  # the ramp inside the table
     layer(r=right(heads=3, kv_heads=3, dim=40, vdim=7, conv=1), ff=0, left_scale=0.0),       # key size over several lanes, one tap
     layer(r=right(heads=1, kv_heads=1, dim=8, vdim=8, conv=5), ff=0, left_scale=0.0),        # one head, all sizes equal
     layer(r=right(heads=6, kv_heads=2, dim=16, vdim=33), ff=0, left_scale=0.0),              # three value heads per key head
     layer(ff=56, left_scale=0.0, right_scale=1.0),
-], ids=["pair", "left", "right", "left_plain_heads", "left_one_head_window1", "left_no_window_cap_rot", "left_ramp", "right_wide_key", "right_one_head",
+], ids=["pair", "left", "right", "left_plain_heads", "left_one_head_window1", "left_no_window_cap_rot", "left_long_window", "left_ramp", "right_wide_key", "right_one_head",
         "right_grouped", "ff"])
 def test_single_layer_prompt(ctx, ly, f32):
     cfg = config([ly], width=32)
@@ -274,6 +275,65 @@ def test_slow_decay_keeps_the_first_tokens(ctx):
     m = build(ctx, cfg, W, True, max_seq=320)
     assert rel(run_cut(m, toks, [64, 64, 1, 2, 1, 1, 3, 64, 2]), want) < TOL[True]  # ... then 98 decoded one by one
     m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_decode_with_the_keys_split_over_ctas(ctx, f32):
+    """a window of 520 positions: decoding beyond position 512 deals a token's keys to two CTAs per head, merged with the sink afterwards;
+    the ring (520 + 63 rows) wraps inside the decoded part"""
+    cfg = config([layer(left(heads=4, kv_heads=2, dim=16, vdim=24, window=520, softcap=10.0, rot_dims=8), ff=0, left_scale=1.0, right_scale=0.3)])
+    W = weights(cfg, seed=18, q_gain=5.0, sink=3.0)
+    toks = tokens(640, cfg["vocab"], 19)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, f32, max_seq=700)
+    assert close(run_cut(m, toks, [64] * 9 + [3, 2]), want, f32)  # 581 in portions, then 59 decoded one by one
+    m.close()
+
+
+def test_rotation_layouts_and_plain_attention_kernels(ctx):
+    """the two kernels on their own with the options that this stack does not use: pairs (i, i + dims/2), no norm weights, no cap, no sink, an
+    output factor, a float ring"""
+    import ctypes as C
+    rs = np.random.RandomState(5)
+    M, H, G, dk, dv, rot, ring = 9, 4, 2, 12, 7, 8, 16
+    nq, nk, nv = H * dk, G * dk, G * dv
+    x = rs.randn(M, nq + nk + nv).astype(np.float32)
+    freq = (50.0 ** (-2.0 * np.arange(rot // 2) / rot)).astype(np.float64)
+    pos = np.arange(M, dtype=np.int32) + 3
+    xd, fd, pd, sd = ctx.array(x), ctx.array(freq), ctx.array(pos), ctx.array(np.zeros(M, dtype=np.int32))
+    cache = ctx.zeros(ring * (nk + nv) * 4)
+    ctx.check(ctx.lib.kf_qk_prepare(ctx.h, xd.ptr, nq + nk + nv, nq, nk, nv, dk, None, None, 1e-5, rot, fd.ptr, 1.5, 1, cache.ptr, 1, ring * (nk + nv), ring, None,
+                                    pd.ptr, sd.ptr, M), "kf_qk_prepare")
+
+    def turn(v, p):  # v [heads, dk]
+        out = v.astype(np.float64).copy()
+        a = p * freq
+        lo, hi = v[:, :rot // 2].astype(np.float64), v[:, rot // 2:rot].astype(np.float64)
+        out[:, :rot // 2] = 1.5 * (lo * np.cos(a) - hi * np.sin(a))
+        out[:, rot // 2:rot] = 1.5 * (hi * np.cos(a) + lo * np.sin(a))
+        return out
+
+    q = np.stack([turn(x[t, :nq].reshape(H, dk), pos[t]) for t in range(M)])
+    k = np.stack([turn(x[t, nq:nq + nk].reshape(G, dk), pos[t]) for t in range(M)])
+    v = x[:, nq + nk:].reshape(M, G, dv).astype(np.float64)
+    got_q = xd.numpy(np.float32, (M, nq + nk + nv))[:, :nq].reshape(M, H, dk)
+    assert np.abs(got_q - q).max() < 2e-6 * np.abs(q).max()
+    rows = cache.numpy(np.float32, (ring, nk + nv))
+    for t in range(M):
+        assert np.abs(rows[pos[t] % ring, :nk].reshape(G, dk) - k[t]).max() < 2e-6 * np.abs(k).max()
+        assert np.array_equal(rows[pos[t] % ring, nk:], x[t, nq + nk:])
+    # attention of the last token over the M rows in the ring (positions 3 .. 3 + M - 1: a sequence that was joined late sees what is there)
+    out = ctx.empty(M * H * dv * 4)
+    last = ctx.array(np.array([pos[-1]], dtype=np.int32))
+    qlast = ctx.array(np.ascontiguousarray(got_q[-1].reshape(1, nq)))
+    ctx.check(ctx.lib.kf_attn_window(ctx.h, out.ptr, 1, H * dv, qlast.ptr, nq, cache.ptr, 1, ring * (nk + nv), ring, None, last.ptr, sd.ptr, 1, H, G, dk, dv, 0.3, 0.0,
+                                     M, 0, 0.5), "kf_attn_window")
+    got = out.numpy(np.float32, (M, H * dv))[0].reshape(H, dv)
+    for h in range(H):
+        g = h // (H // G)
+        s = (k[:, g] @ q[-1, h]) * 0.3
+        w = np.exp(s - s.max())
+        assert np.abs(got[h] - 0.5 * (w[:, None] * v[:, g]).sum(0) / w.sum()).max() < 1e-5
 
 
 # ------------------------------------------------------------------------------------------------------------ entry points
