@@ -38,10 +38,10 @@ def _sources():
 def _digest(paths):
     h = hashlib.sha256()
     for p in sorted(paths):
-        h.update(p.encode())
+        h.update(os.path.relpath(p, ROOT).encode())  # relative: a checkout moved or copied elsewhere with its built library does not rebuild
         with open(p, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS).replace(ROOT, ".").encode())
     return h.hexdigest()
 
 
