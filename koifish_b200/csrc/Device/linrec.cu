@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
 #pragma unroll
     for (int i = 0; i < NPT; i++) S[i] = (live && n0 + i < dk && !fresh) ? st[n0 + i] : 0.f;
     const float Aexp = a.decay_kind == 1 ? expf(bf16_bits_to_f32(a.A_log[h])) : 0.f;
+    const bool zh = a.z_head != 0;  // one decay per head and token: formed once per staged token (sG[tt]), not per key channel
     const int warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
     for (int t0 = 0; t0 < a.T; t0 += TB) {
         const int nt = min(TB, a.T - t0);
@@ -83,8 +84,7 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
                     const int tt = i / dk, n = i - tt * dk;
                     const size_t m = (size_t)(m0 + t0 + tt);
                     kv[e] = a.k[m * a.ldk + kh * dk + n], qv[e] = a.q[m * a.ldq + kh * dk + n];
-                    const int zi = a.z_head ? h : h * dk + n;
-                    zv[e] = a.z[m * a.ldz + zi] + (a.zbias ? bf16_bits_to_f32(a.zbias[zi]) : 0.f);
+                    if (!zh) zv[e] = a.z[m * a.ldz + h * dk + n] + (a.zbias ? bf16_bits_to_f32(a.zbias[h * dk + n]) : 0.f);
                 }
             }
 #pragma unroll
@@ -93,10 +93,15 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
                 if (i < nt * dk) {
                     const int tt = i / dk, o = tt * dkp + ix(i - tt * dk);
                     sK[o] = kv[e], sQ[o] = qv[e];
-                    sG[o] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zv[e])) : expf(log_sigmoid_f(zv[e]) * a.inv_tau);
+                    if (!zh) sG[o] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(zv[e])) : expf(log_sigmoid_f(zv[e]) * a.inv_tau);
                 }
             }
         }
+        if (zh)
+            for (int i = tid; i < nt; i += blockDim.x) {
+                const float z = a.z[(size_t)(m0 + t0 + i) * a.ldz + h] + (a.zbias ? bf16_bits_to_f32(a.zbias[h]) : 0.f);
+                sG[i] = a.decay_kind == 1 ? expf(-Aexp * softplus_f(z)) : expf(log_sigmoid_f(z) * a.inv_tau);
+            }
         for (int i0 = tid; i0 < nt * PB; i0 += 4 * blockDim.x) {
             float vv[4];
 #pragma unroll
@@ -141,17 +146,27 @@ __global__ void __launch_bounds__(256) kf_gated_scan_kernel(ScanArgs a) {
                 const float4* g4 = reinterpret_cast<const float4*>(sG + tt * dkp + ix(n0));
 #pragma unroll
                 for (int j = 0; j < NPT / 4; j++) {
-                    const float4 kv = k4[j], qv = q4[j], gv = g4[j];
+                    const float4 kv = k4[j], qv = q4[j];
                     kk[4 * j] = kv.x, kk[4 * j + 1] = kv.y, kk[4 * j + 2] = kv.z, kk[4 * j + 3] = kv.w;
                     qq[4 * j] = qv.x, qq[4 * j + 1] = qv.y, qq[4 * j + 2] = qv.z, qq[4 * j + 3] = qv.w;
-                    gg[4 * j] = gv.x, gg[4 * j + 1] = gv.y, gg[4 * j + 2] = gv.z, gg[4 * j + 3] = gv.w;
+                }
+                if (zh) {
+                    const float gh = sG[tt];
+#pragma unroll
+                    for (int i = 0; i < NPT; i++) gg[i] = gh;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NPT / 4; j++) {
+                        const float4 gv = g4[j];
+                        gg[4 * j] = gv.x, gg[4 * j + 1] = gv.y, gg[4 * j + 2] = gv.z, gg[4 * j + 3] = gv.w;
+                    }
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < NPT; i++) {
                     const bool in = n0 + i < dk;
                     const int o = tt * dkp + ix(n0 + i);
-                    kk[i] = in ? sK[o] : 0.f, qq[i] = in ? sQ[o] : 0.f, gg[i] = in ? sG[o] : 1.f;
+                    kk[i] = in ? sK[o] : 0.f, qq[i] = in ? sQ[o] : 0.f, gg[i] = in ? sG[zh ? tt : o] : 1.f;
                 }
             }
             const float vv = sV[tt * PB + (pl < PB ? pl : 0)];
