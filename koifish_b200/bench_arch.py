@@ -68,14 +68,14 @@ def kivorax_config(p):
 
 
 def sedotar_config(p):
-    """every layer: attention (head size 128, 4 query heads per kv head, half of each head rotated, window, cap 30, sink) beside the delta
+    """every layer: attention (head size 128, 4 query heads per kv head, half of each head rotated, window, cap 50, sink) beside the delta
     rule (as many value heads of 128, half as many key heads of 64), then the relu-gated feed-forward"""
     w, d = p["width"], p["sdt"]
-    lf = dict(heads=d["heads"], kv_heads=d["kv_heads"], dim=128, vdim=128, conv=4, scale=128 ** -0.5, softcap=30.0, mask=dict(size=d["window"]),
-              rot=dict(base=1e6, dims=64, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    lf = dict(heads=d["heads"], kv_heads=d["kv_heads"], dim=128, vdim=128, conv=4, scale=128 ** -0.5, softcap=50.0, mask=dict(size=d["window"]),
+              rot=dict(base=1e6, dims=64, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0)))
     rt = dict(heads=d["heads"], kv_heads=d["heads"] // 2, dim=64, vdim=128, conv=4)
     ly = {"type": "parallel", "mixer": {"left": lf, "right": rt, "left_scale": 0.7, "right_scale": 0.7}, "mlp": {"kind": "dense", "ff": d["ff"]}}
-    return {"architecture": "Sedotar", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": [ly] * len(p["pattern"])}
+    return {"architecture": "Sedotar", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": [ly] * len(p["pattern"])}
 
 
 def kivorax_dense_config(p):

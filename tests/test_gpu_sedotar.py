@@ -76,7 +76,7 @@ def run_cut(model, toks, cuts, slot=0):
 
 
 def edited(cfg, fn):
-    """a copy of cfg whose first layer's attention card went through fn"""
+    """a copy of cfg whose first layer's attention settings went through fn"""
     c = json.loads(json.dumps(cfg))
     fn(c["layers"][0]["mixer"]["left"])
     return c
@@ -235,7 +235,7 @@ def test_window_edges_cap_and_sink(ctx, f32):
     The framework then has to match in prompt panels (edges inside a panel and across panels), in small portions and in decoding, over
     more than five turns of the ring (23 + 64 - 1 rows)."""
     cfg = config([layer(left(heads=4, kv_heads=2, dim=16, vdim=12, window=23, softcap=6.0, rot_dims=12, base=100.0), ff=0, left_scale=1.0, right_scale=0.3),
-                  layer(left(window=40), ff=24)])
+                  layer(left(window=37), ff=24)])
     W = weights(cfg, seed=9, q_gain=12.0, sink=5.0)
     toks = tokens(520, cfg["vocab"], 7)
     want = oracle(cfg, W, toks)
