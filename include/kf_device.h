@@ -371,6 +371,47 @@ int kf_attn_window_prefill(kf_ctx* ctx, void* out_bf16_dev, int ldo, const void*
                            const void* sink_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale,
                            float softcap, int window, float out_scale);
 
+/* ---- pre-norm stacks with a channel-wise gated recurrence, sigmoid-weighted attention inside blocks of positions, latent attention with
+ *      stretched rotation frequencies, clamped gated feed-forwards and group-limited expert routing (ops_f32.cu, linrec.cu, attn_window.cu,
+ *      seqmix.cu); no reference equivalents ---- */
+/* res[rows][dim] += a + b + vec (a, b: float rows or NULL; vec: bf16 [dim] or NULL); act_out = rmsnorm(res) * w in the activation type
+ * (w NULL: the sum only) -- the residual add of one sublayer and the norm of the next in one launch */
+int kf_residual_prenorm(kf_ctx* ctx, float* res_dev, void* act_out_dev, int act_f32, const float* a_dev, int lda, const float* b_dev, int ldb,
+                        const void* vec_bf16_dev, const void* w_bf16_dev, int rows, int dim, float eps);
+/* out = g' * sigmoid(alpha * g') * (u' + shift) in the activation type, g' = min(gate, limit), u' = clamp(up, -limit, limit) (limit <= 0: no clamp) */
+int kf_glu_clamped(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* gate_dev, int ldg, const float* up_dev, int ldu, int rows, int cols,
+                   float limit, float alpha, float shift);
+int kf_scale_f32(kf_ctx* ctx, float* x_dev, size_t n, float s); /* x *= s */
+/* kf_moe_route's tables from sigmoid scores: the choice runs over sigmoid(logit) + choice_bias inside the `keep` best of `groups` equal groups
+ * of neighbouring experts (a group ranks by the sum of its two largest choice values); weights = scale * sigmoid(logit), not renormalised */
+int kf_moe_route_grouped(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
+                         int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* choice_bias_bf16_dev, int M, int E, int top,
+                         int groups, int keep, float scale);
+/* minGRU: z = sigmoid(z_logit + zb), u = x_logit + xb, c = u + 1/2 (u >= 0) | sigmoid(u); s <- (1 - z) s + z c per channel; out = s * silu(g_logit)
+ * in the activation type; state float [slot][width], zero at position 0 */
+int kf_mingru(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* z_logit_dev, int ldz, const void* z_bias_bf16_dev, const float* x_logit_dev, int ldx,
+              const void* x_bias_bf16_dev, const float* g_logit_dev, int ldg, float* state_dev, size_t state_stride, const int32_t* pos_dev,
+              const int32_t* slot_dev, int nseq, int T, int width);
+/* kf_qk_prepare with biases on q and k (added first) and, with v_from_k, values that are the keys before the rotation (x = [q | k], nv == nk) */
+int kf_qk_prepare_ex(kf_ctx* ctx, float* x_dev, int ldx, int nq, int nk, int nv, int head_dim, const void* q_bias_bf16_dev, const void* k_bias_bf16_dev,
+                     int v_from_k, const void* q_norm_bf16_dev, const void* k_norm_bf16_dev, float eps, int rot_dims, const double* inv_freq_dev, float amp,
+                     int layout, void* cache_dev, int cache_f32, size_t slot_stride, int ring, void* q_bf16_out_dev, const int32_t* pos_dev,
+                     const int32_t* slot_dev, int M);
+/* out = sum over the visible keys of sigmoid(scale q . k + head_bias[h]) v, not normalised; visible: positions <= pos inside the block of `block`
+ * positions (counted from 0) that holds pos (block <= 0: none) and inside the last `window` positions (window <= 0: none); ring cache as kf_attn_window */
+int kf_attn_sigmoid(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const void* cache_dev, int cache_f32, size_t slot_stride,
+                    int ring, const void* head_bias_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
+                    int block, int window, int max_keys_hint, float out_scale);
+/* kf_latent_append / kf_latent_attention with the rotation's pair layout (0: (i, i + dims/2); 1: (2i, 2i+1)), a factor on cosine and sine, and an
+ * optional sink (NULL: plain softmax) */
+int kf_latent_append_ex(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride, const float* ckr_dev, int ldc, const void* norm_w_bf16_dev,
+                        const double* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims, float eps,
+                        int layout, float amp);
+int kf_latent_attention_ex(kf_ctx* ctx, float* lat_out_dev, float* qa_work_dev, const float* q_dev, int ldq, const void* w_uk_bf16_dev,
+                           const void* sink_bf16_dev, const void* cache_dev, int cache_f32, size_t slot_stride, const double* inv_freq_dev,
+                           const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale,
+                           int max_pos_hint, int layout, float amp);
+
 #ifdef __cplusplus
 }
 #endif

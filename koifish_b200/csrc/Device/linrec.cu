@@ -299,7 +299,76 @@ __global__ void __launch_bounds__(32 * LRU_W) kf_rglru_scan_kernel(TO* __restric
     }
     if (w == W - 1) *st = s;  // the last run ends at token T - 1 (runs may be empty only at the end when T < W, which the launch rules out)
 }
+// minGRU: a channel-wise gated recurrence whose gates read only the current token,
+//     z = sigmoid(zl + zb),   u = xl + xb,   c = u + 1/2 (u >= 0) | sigmoid(u) (u < 0),   s <- (1 - z) s + z c,   out = s * silu(gl)
+// with 1 - z formed as sigmoid(-(zl + zb)).  Same launch shape as kf_rglru_scan_kernel: a CTA owns 32 channels, its warps runs of consecutive
+// tokens; a first pass reduces every run to one affine map, a second replays it from the run's incoming state.  The gates are recomputed
+// in the second pass (no work buffer).
+template <typename TO>
+__global__ void __launch_bounds__(32 * LRU_W) kf_mingru_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ zl, int ldz, const uint16_t* __restrict__ zb,
+                                                               const float* __restrict__ xl, int ldx, const uint16_t* __restrict__ xb,
+                                                               const float* __restrict__ gl, int ldg, float* __restrict__ state, size_t state_stride,
+                                                               const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int T, int width) {
+    __shared__ float sP[LRU_W][32], sB[LRU_W][32];
+    const int seq = blockIdx.y, lane = threadIdx.x & 31, w = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int ch = blockIdx.x * 32 + lane, m0 = seq * T;
+    const bool live = ch < width;
+    const int run = (T + W - 1) / W, t_lo = min(T, w * run), t_hi = min(T, t_lo + run);
+    float* st = state + (size_t)slot[m0] * state_stride + (live ? ch : 0);
+    float s = (pos[m0] == 0 || !live) ? 0.f : *st;
+    const float bz = (live && zb) ? bf16_bits_to_f32(zb[ch]) : 0.f, bx = (live && xb) ? bf16_bits_to_f32(xb[ch]) : 0.f;
+    auto gates = [&](size_t m, float& keep, float& add) {
+        const float zv = zl[m * ldz + ch] + bz, u = xl[m * ldx + ch] + bx;
+        keep = sigmoid_f(-zv);
+        add  = sigmoid_f(zv) * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
+    };
+    float P = 1.f, B = 0.f;
+    if (W > 1 && live) {
+#pragma unroll 4
+        for (int t = t_lo; t < t_hi; t++) {
+            float keep, add;
+            gates((size_t)(m0 + t), keep, add);
+            B = fmaf(keep, B, add);
+            P *= keep;
+        }
+    }
+    sP[w][lane] = P, sB[w][lane] = B;
+    __syncthreads();
+    for (int q = 0; q < w; q++) s = fmaf(sP[q][lane], s, sB[q][lane]);
+    if (!live) return;
+#pragma unroll 4
+    for (int t = t_lo; t < t_hi; t++) {
+        const size_t m = (size_t)(m0 + t);
+        float keep, add;
+        gates(m, keep, add);
+        s = fmaf(keep, s, add);
+        const float g = gl[m * ldg + ch];
+        const float o = s * g * sigmoid_f(g);
+        if (sizeof(TO) == 2) ((uint16_t*)out)[m * ldo + ch] = f32_to_bf16_bits(o);
+        else ((float*)out)[m * ldo + ch] = o;
+    }
+    if (t_hi == T && t_lo < T) *st = s;  // the run that ends at the last token leaves the state
+}
 }  // namespace
+
+// minGRU over nseq x T tokens: z_logit, x_logit, g_logit float rows [M][ld*] of `width` channels (bf16 biases of the first two, or NULL);
+// out [M][ldo] = s * silu(g) in the activation type; state: float [slot][width], started from zero at position 0.
+extern "C" int kf_mingru(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* z_logit, int ldz, const void* z_bias_bf16, const float* x_logit, int ldx,
+                         const void* x_bias_bf16, const float* g_logit, int ldg, float* state, size_t state_stride, const int32_t* pos_dev,
+                         const int32_t* slot_dev, int nseq, int T, int width) {
+    if (!ctx || !out || !z_logit || !x_logit || !g_logit || !state || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && width >= 1 && state_stride >= (size_t)width, "shape");
+    dim3 grid((width + 31) / 32, nseq);
+    const int warps = std::max(1, std::min(LRU_W, T / 8)), threads = 32 * warps;  // runs of at least 8 tokens; one warp when decoding
+    if (out_f32)
+        kf_mingru_kernel<float><<<grid, threads, 0, ctx->stream>>>((float*)out, ldo, z_logit, ldz, (const uint16_t*)z_bias_bf16, x_logit, ldx,
+                                                               (const uint16_t*)x_bias_bf16, g_logit, ldg, state, state_stride, pos_dev, slot_dev, T, width);
+    else
+        kf_mingru_kernel<uint16_t><<<grid, threads, 0, ctx->stream>>>((uint16_t*)out, ldo, z_logit, ldz, (const uint16_t*)z_bias_bf16, x_logit, ldx,
+                                                                  (const uint16_t*)x_bias_bf16, g_logit, ldg, state, state_stride, pos_dev, slot_dev, T, width);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
 
 // Matrix-state recurrence over nseq x T tokens (see the head of this file).  q, k: float rows with G kv heads of dk entries at row strides
 // ldq / ldk; v: H heads of dv entries; z: decay logits H x dk (+ bf16 bias zbias or NULL); beta_logit: H per token (delta rule only).

@@ -144,19 +144,130 @@ __global__ void __launch_bounds__(256) kf_postnorm_residual_kernel(float* __rest
     }
 }
 
+// Pre-norm residual step of one row:  res += a + b + vec (each optional);  act_out = res / sqrt(mean(res^2) + eps) * w in the activation
+// type (what the next sublayer's matmul reads; w NULL: only the sum).
+template <typename TO>
+__global__ void __launch_bounds__(256) kf_residual_prenorm_kernel(float* __restrict__ res, TO* __restrict__ act_out, const float* __restrict__ a, int lda,
+                                                                  const float* __restrict__ b, int ldb, const uint16_t* __restrict__ vec,
+                                                                  const uint16_t* __restrict__ w, int dim, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float* xr = res + (size_t)r * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = xr[i];
+        if (a) v += a[(size_t)r * lda + i];
+        if (b) v += b[(size_t)r * ldb + i];
+        if (vec) v += bf16_bits_to_f32(vec[i]);
+        if (a || b || vec) xr[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!w) return;
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {  // a thread re-reads what it wrote itself
+        const float v = xr[i] * s * bf16_bits_to_f32(w[i]);
+        if (sizeof(TO) == 2) ((uint16_t*)act_out)[(size_t)r * dim + i] = f32_to_bf16_bits(v);
+        else ((float*)act_out)[(size_t)r * dim + i] = v;
+    }
+}
+// out = g' * sigmoid(alpha * g') * (u' + shift),  g' = min(g, limit), u' = clamp(u, -limit, limit)  (limit <= 0: not clamped)
+template <typename TO>
+__global__ void kf_glu_clamped_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ g, int ldg, const float* __restrict__ u, int ldu, int cols,
+                                      float limit, float alpha, float shift) {
+    const int r = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < cols; c += gridDim.x * blockDim.x) {
+        float gv = g[(size_t)r * ldg + c], uv = u[(size_t)r * ldu + c];
+        if (limit > 0.f) gv = fminf(gv, limit), uv = fminf(fmaxf(uv, -limit), limit);
+        const float v = gv * sigmoid_f(alpha * gv) * (uv + shift);
+        if (sizeof(TO) == 2) ((uint16_t*)out)[(size_t)r * ldo + c] = f32_to_bf16_bits(v);
+        else ((float*)out)[(size_t)r * ldo + c] = v;
+    }
+}
+__global__ void kf_scale_f32_kernel(float* __restrict__ x, size_t n, float s) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+
 __global__ void kf_f32_to_bf16_kernel(uint16_t* __restrict__ out, const float* __restrict__ in, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = f32_to_bf16_bits(in[i]);
 }
 
 // ---- mixture of experts ---------------------------------------------------------------------------------------------------
+// How a token's experts are chosen and weighted.  kind 0: arg-max over logits (+ bias), weights from a softmax (the kernels' `full` flag).
+// kind 1: scores s = sigmoid(logit); the choice runs over s + bias; the experts form `groups` equal groups of neighbours, a group is ranked
+// by the sum of its two largest choice values and only the `keep` best groups can be chosen from; weights = scale * s of the chosen, not
+// renormalised.
+struct RouteMode {
+    int kind, groups, keep;
+    float scale;
+};
+// one warp routes one token in kind 1.  taken: the token's chosen experts so far (shared or global memory, written by lane 0).
+__device__ __forceinline__ void route_grouped_warp(int* taken, int32_t* idx, float* __restrict__ wgt, const float* __restrict__ lg,
+                                                   const uint16_t* __restrict__ bias, int E, int top, const RouteMode md, int lane) {
+    const int per = E / md.groups;
+    // lane g keeps the rank value of group g (groups <= 32): the two largest choice values of the group, found by all lanes together
+    float gscore = -INFINITY;
+    for (int g = 0; g < md.groups; g++) {
+        float a = -INFINITY, b = -INFINITY;  // largest, second largest of this lane's share
+        for (int e = g * per + lane; e < (g + 1) * per; e += 32) {
+            const float v = sigmoid_f(lg[e]) + (bias ? bf16_bits_to_f32(bias[e]) : 0.f);
+            if (v > a) b = a, a = v;
+            else if (v > b) b = v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+            const float hi = fmaxf(a, oa), lo = fmaxf(fminf(a, oa), fmaxf(b, ob));
+            a = hi, b = lo;
+        }
+        if (lane == g) gscore = per > 1 ? a + b : a;
+    }
+    unsigned kept = 0;
+    for (int r = 0; r < md.keep; r++) {
+        float best = (lane < md.groups && !((kept >> lane) & 1u)) ? gscore : -INFINITY;
+        int bi     = (lane < md.groups && !((kept >> lane) & 1u)) ? lane : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi   = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) best = ob, bi = oi;
+        }
+        if (bi != 0x7fffffff) kept |= 1u << bi;
+    }
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi     = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            if (!((kept >> (e / per)) & 1u)) continue;
+            bool was = false;
+            for (int q = 0; q < j; q++) was = was || taken[q] == e;
+            if (was) continue;
+            const float v = sigmoid_f(lg[e]) + (bias ? bf16_bits_to_f32(bias[e]) : 0.f);
+            if (bi == 0x7fffffff || v > best || (v == best && e < bi)) best = v, bi = e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi   = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) best = ob, bi = oi;
+        }
+        if (lane == 0) taken[j] = bi, idx[j] = bi, wgt[j] = md.scale * sigmoid_f(lg[bi]);
+        __syncwarp();
+    }
+}
 // one warp per token: `top` rounds of arg-max over the E router logits (+ bias), ties to the lower index; weights = softmax over the
 // chosen logits only, or (full) the chosen entries of the softmax over ALL experts, not renormalised.  All in fp32.
 __global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, const float* __restrict__ logits, int ldl,
-                                                           const uint16_t* __restrict__ bias, int M, int E, int top, int full) {
+                                                           const uint16_t* __restrict__ bias, int M, int E, int top, int full, const RouteMode md) {
     const int m = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (m >= M) return;
     const float* lg = logits + (size_t)m * ldl;
+    if (md.kind == 1) {
+        route_grouped_warp(idx + (size_t)m * top, idx + (size_t)m * top, wgt + (size_t)m * top, lg, bias, E, top, md, lane);
+        return;
+    }
     float first = 0.f, den = 0.f;
     for (int j = 0; j < top; j++) {
         float best = -INFINITY;
@@ -195,12 +306,16 @@ constexpr int kRouteSmall = 256;
 __global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, int32_t* __restrict__ offsets,
                                                                  int32_t* __restrict__ entry_slot, int32_t* __restrict__ slot_row,
                                                                  int32_t* __restrict__ slot_group, const float* __restrict__ logits, int ldl,
-                                                                 const uint16_t* __restrict__ bias, int M, int E, int top, int full) {
+                                                                 const uint16_t* __restrict__ bias, int M, int E, int top, int full, const RouteMode md) {
     __shared__ int sidx[kRouteSmall];
     __shared__ int srank[kRouteSmall];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = M * top;
     for (int m = warp; m < M; m += 8) {
         const float* lg = logits + (size_t)m * ldl;
+        if (md.kind == 1) {
+            route_grouped_warp(sidx + m * top, idx + (size_t)m * top, wgt + (size_t)m * top, lg, bias, E, top, md, lane);
+            continue;
+        }
         float first = 0.f, den = 0.f;
         for (int j = 0; j < top; j++) {
             float best = -INFINITY;
@@ -419,6 +534,38 @@ extern "C" int kf_postnorm_residual(kf_ctx* ctx, float* res, void* act_out, int 
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
+// res[rows][dim] += a + b + vec (a, b: float rows or NULL; vec: bf16 [dim] or NULL); act_out (with w_bf16) = rmsnorm(res) * w in the
+// activation type.  w_bf16 NULL: the sum only.
+extern "C" int kf_residual_prenorm(kf_ctx* ctx, float* res, void* act_out, int act_f32, const float* a, int lda, const float* b, int ldb, const void* vec_bf16,
+                                   const void* w_bf16, int rows, int dim, float eps) {
+    if (!ctx || !res || (w_bf16 && !act_out)) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && dim >= 1, "shape");
+    if (!w_bf16 && !a && !b && !vec_bf16) return KF_OK;
+    if (act_f32)
+        kf_residual_prenorm_kernel<float><<<rows, 256, 0, ctx->stream>>>(res, (float*)act_out, a, lda, b, ldb, (const uint16_t*)vec_bf16, (const uint16_t*)w_bf16, dim, eps);
+    else
+        kf_residual_prenorm_kernel<uint16_t><<<rows, 256, 0, ctx->stream>>>(res, (uint16_t*)act_out, a, lda, b, ldb, (const uint16_t*)vec_bf16, (const uint16_t*)w_bf16, dim, eps);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+// out[rows][ldo] (activation type) = g' * sigmoid(alpha * g') * (u' + shift) with g' = min(gate, limit), u' = clamp(up, -limit, limit); limit <= 0: no clamp
+extern "C" int kf_glu_clamped(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* gate, int ldg, const float* up, int ldu, int rows, int cols, float limit,
+                              float alpha, float shift) {
+    if (!ctx || !out || !gate || !up) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, rows >= 1 && cols >= 1, "shape");
+    dim3 grid(std::min(64, (cols + 255) / 256), rows);
+    if (out_f32) kf_glu_clamped_kernel<float><<<grid, 256, 0, ctx->stream>>>((float*)out, ldo, gate, ldg, up, ldu, cols, limit, alpha, shift);
+    else kf_glu_clamped_kernel<uint16_t><<<grid, 256, 0, ctx->stream>>>((uint16_t*)out, ldo, gate, ldg, up, ldu, cols, limit, alpha, shift);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+extern "C" int kf_scale_f32(kf_ctx* ctx, float* x, size_t n, float s) {
+    if (!ctx || !x) return KF_ERR_BAD_ARG;
+    if (!n || s == 1.f) return KF_OK;
+    kf_scale_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, n, s);
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
 extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size_t n) {
     if (!ctx || !out_bf16 || !in) return KF_ERR_BAD_ARG;
     if (!n) return KF_OK;
@@ -431,18 +578,18 @@ extern "C" int kf_f32_to_bf16(kf_ctx* ctx, void* out_bf16, const float* in, size
 // offsets [E + 1], entry_slot [M * top] (where each (token, choice) sits among the expert-sorted slots), slot_row / slot_group [M * top].
 // work: device int32 scratch of 2 * M * top + E entries.
 // full_softmax 0: weights = softmax over the chosen logits; 1: the chosen entries of the softmax over all E experts (not renormalised).
-extern "C" int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
-                               int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top, int full_softmax) {
+static int moe_route_impl(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                          int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top, int full_softmax, const RouteMode md) {
     if (!ctx || !idx || !wgt || !offsets || !entry_slot || !slot_row || !slot_group || !work || !logits) return KF_ERR_BAD_ARG;
     KF_REQUIRE(ctx, M >= 1 && E >= 1 && top >= 1 && top <= E && ldl >= E, "1 <= top <= experts");
     const int n = M * top;
     if (n <= kRouteSmall && (long long)E * n <= 16384) {
-        kf_moe_route_small_kernel<<<1, 256, 0, ctx->stream>>>(idx, wgt, offsets, entry_slot, slot_row, slot_group, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax);
+        kf_moe_route_small_kernel<<<1, 256, 0, ctx->stream>>>(idx, wgt, offsets, entry_slot, slot_row, slot_group, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax, md);
         KF_LAUNCH_CHECK(ctx);
         return KF_OK;
     }
     int32_t *rank = work, *count = work + n;
-    kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax);
+    kf_moe_route_kernel<<<(M + 3) / 4, 128, 0, ctx->stream>>>(idx, wgt, logits, ldl, (const uint16_t*)bias_bf16, M, E, top, full_softmax, md);
     KF_LAUNCH_CHECK(ctx);
     kf_moe_rank_kernel<<<E, 256, 0, ctx->stream>>>(rank, count, idx, n);
     KF_LAUNCH_CHECK(ctx);
@@ -451,6 +598,23 @@ extern "C" int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* o
     kf_moe_slots_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(entry_slot, slot_row, slot_group, idx, rank, offsets, n, top);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
+}
+extern "C" int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                               int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top, int full_softmax) {
+    const RouteMode md = {0, 1, 1, 1.f};
+    return moe_route_impl(ctx, idx, wgt, offsets, entry_slot, slot_row, slot_group, work, logits, ldl, bias_bf16, M, E, top, full_softmax, md);
+}
+// The same tables from sigmoid scores: the choice runs over sigmoid(logit) + choice_bias (bf16 [E] or NULL) inside the `keep` best of
+// `groups` equal groups of neighbouring experts (a group ranks by the sum of its two largest choice values; groups <= 32, groups 1: no
+// grouping); weights = scale * sigmoid(logit) of the chosen experts, not renormalised.  top <= keep * (E / groups).
+extern "C" int kf_moe_route_grouped(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
+                                    int32_t* work, const float* logits, int ldl, const void* choice_bias_bf16, int M, int E, int top, int groups, int keep,
+                                    float scale) {
+    if (!ctx) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, groups >= 1 && groups <= 32 && E >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && top >= 1 && top <= keep * (E / groups),
+               "groups <= 32 divide the experts; 1 <= keep <= groups; top <= keep * experts / groups");
+    const RouteMode md = {1, groups, keep, scale};
+    return moe_route_impl(ctx, idx, wgt, offsets, entry_slot, slot_row, slot_group, work, logits, ldl, choice_bias_bf16, M, E, top, 0, md);
 }
 extern "C" int kf_moe_route(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
                             int32_t* work, const float* logits, int ldl, const void* bias_bf16, int M, int E, int top) {

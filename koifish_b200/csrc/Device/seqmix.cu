@@ -180,7 +180,7 @@ template <typename TC>
 __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ cache, size_t slot_stride, const float* __restrict__ ckr, int ldc,
                                                                const uint16_t* __restrict__ w, const double* __restrict__ inv_freq,
                                                                const int32_t* __restrict__ pos, const int32_t* __restrict__ slot, int rank, int rot_dim,
-                                                               int dims, float eps) {
+                                                               int dims, float eps, int pairs, float amp) {
     __shared__ float red[32];
     const int m = blockIdx.x, W = rank + rot_dim;
     const float* in = ckr + (size_t)m * ldc;
@@ -199,11 +199,13 @@ __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ 
     for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
         float v = in[rank + i];
         if (i < dims) {
-            const int j = i < half ? i : i - half;
+            // pairs 0: entry j turns with entry j + dims/2; 1: entry 2j with entry 2j + 1.  first: this entry is the first of its pair
+            const bool first = pairs ? !(i & 1) : i < half;
+            const int j = pairs ? i >> 1 : (first ? i : i - half);
             double sn, cs;
             sincos((double)fp * inv_freq[j], &sn, &cs);  // angle, sine and cosine in double
-            const float a = in[rank + j], b = in[rank + j + half];
-            v = i < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
+            const float a = in[rank + (pairs ? 2 * j : j)], b = in[rank + (pairs ? 2 * j + 1 : j + half)];
+            v = (first ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn) * amp;
         }
         put(rank + i, v);
     }
@@ -213,7 +215,7 @@ __global__ void __launch_bounds__(256) kf_latent_append_kernel(TC* __restrict__ 
 constexpr int QT = 8;
 __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict__ qa, const float* __restrict__ q, int ldq, const uint16_t* __restrict__ Wuk,
                                                               const double* __restrict__ inv_freq, const int32_t* __restrict__ pos, int M, int H, int dn,
-                                                              int rot_dim, int dims, int rank, float scale) {
+                                                              int rot_dim, int dims, int rank, float scale, int pairs, float amp) {
     extern __shared__ float sq[];  // [QT][dn + rot_dim]
     const int m0 = blockIdx.x * QT, h = blockIdx.y, D = dn + rot_dim, W = rank + rot_dim;
     const int nt = min(QT, M - m0);
@@ -242,11 +244,12 @@ __global__ void __launch_bounds__(128) kf_latent_query_kernel(float* __restrict_
         const float* sr = sq + t * D + dn;
         float v = sr[e];
         if (e < dims) {
-            const int j = e < half ? e : e - half;
+            const bool first = pairs ? !(e & 1) : e < half;
+            const int j = pairs ? e >> 1 : (first ? e : e - half);
             double sn, cs;
             sincos((double)pos[m0 + t] * inv_freq[j], &sn, &cs);
-            const float a = sr[j], b = sr[j + half];
-            v = e < half ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn;
+            const float a = sr[pairs ? 2 * j : j], b = sr[pairs ? 2 * j + 1 : j + half];
+            v = (first ? a * (float)cs - b * (float)sn : b * (float)cs + a * (float)sn) * amp;
         }
         qa[((size_t)(m0 + t) * H + h) * W + rank + e] = v * scale;
     }
@@ -299,10 +302,10 @@ __global__ void __launch_bounds__(128) kf_latent_attn_kernel(float* __restrict__
     }
     if (lane == 0) smx[warp] = mx, ssum[warp] = sum;
     __syncthreads();
-    const float sk = bf16_bits_to_f32(sink[h]);
+    const float sk = sink ? bf16_bits_to_f32(sink[h]) : -INFINITY;  // no sink: no extra term in the denominator
     float M4 = sk;
     for (int w = 0; w < 4; w++) M4 = fmaxf(M4, smx[w]);
-    float den = expf(sk - M4), f[4];
+    float den = sink ? expf(sk - M4) : 0.f, f[4];
     for (int w = 0; w < 4; w++) f[w] = smx[w] == -INFINITY ? 0.f : expf(smx[w] - M4), den += ssum[w] * f[w];
     float* o = out + ((size_t)m * H + h) * rank;
     for (int e = threadIdx.x; e < rank; e += blockDim.x) {
@@ -501,12 +504,12 @@ __global__ void __launch_bounds__(128) kf_latent_merge_kernel(float* __restrict_
     const float* ml = part_ml + ((size_t)m * HG * 16 + h) * S * 2;
     const float* po = part_o + ((size_t)m * HG * 16 + h) * S * rank;
     __shared__ float fac[64];  // exp(m_s - M) per split (S <= 64), 0 for an empty split
-    const float sk = bf16_bits_to_f32(sink[h]);
+    const float sk = sink ? bf16_bits_to_f32(sink[h]) : -INFINITY;
     float M = sk;
     for (int s = 0; s < S; s++) M = fmaxf(M, ml[2 * s]);
     if ((int)threadIdx.x < S) fac[threadIdx.x] = ml[2 * threadIdx.x] == -INFINITY ? 0.f : expf(ml[2 * threadIdx.x] - M);
     __syncthreads();
-    float den = expf(sk - M);
+    float den = sink ? expf(sk - M) : 0.f;
     for (int s = 0; s < S; s++) den += ml[2 * s + 1] * fac[s];
     float* o = out + ((size_t)m * H + h) * rank;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
@@ -592,14 +595,21 @@ extern "C" int kf_ssm_scan(kf_ctx* ctx, float* y, int ldy, const float* xbc, con
 extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t slot_stride, const float* ckr, int ldc, const void* norm_w_bf16,
                                 const double* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims,
                                 float eps) {
+    return kf_latent_append_ex(ctx, cache, cache_f32, slot_stride, ckr, ldc, norm_w_bf16, inv_freq_dev, pos_dev, slot_dev, M, rank, rot_dim, rot_dims, eps, 0, 1.f);
+}
+// the same with the pair layout of the rotation (0: entry i with i + rot_dims/2; 1: entry 2i with 2i + 1) and a factor `amp` on cosine and sine
+extern "C" int kf_latent_append_ex(kf_ctx* ctx, void* cache, int cache_f32, size_t slot_stride, const float* ckr, int ldc, const void* norm_w_bf16,
+                                   const double* inv_freq_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int rank, int rot_dim, int rot_dims,
+                                   float eps, int layout, float amp) {
     if (!ctx || !cache || !ckr || !norm_w_bf16 || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, M >= 1 && rank >= 1 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0, "rotated dims: even, <= rot_dim");
+    KF_REQUIRE(ctx, M >= 1 && rank >= 1 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 && (layout == 0 || layout == 1),
+               "rotated dims: even, <= rot_dim");
     if (cache_f32)
         kf_latent_append_kernel<float><<<M, 256, 0, ctx->stream>>>((float*)cache, slot_stride, ckr, ldc, (const uint16_t*)norm_w_bf16, inv_freq_dev, pos_dev,
-                                                                  slot_dev, rank, rot_dim, rot_dims, eps);
+                                                                  slot_dev, rank, rot_dim, rot_dims, eps, layout, amp);
     else
         kf_latent_append_kernel<uint16_t><<<M, 256, 0, ctx->stream>>>((uint16_t*)cache, slot_stride, ckr, ldc, (const uint16_t*)norm_w_bf16, inv_freq_dev,
-                                                                     pos_dev, slot_dev, rank, rot_dim, rot_dims, eps);
+                                                                     pos_dev, slot_dev, rank, rot_dim, rot_dims, eps, layout, amp);
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }
@@ -608,11 +618,22 @@ extern "C" int kf_latent_append(kf_ctx* ctx, void* cache, int cache_f32, size_t 
 extern "C" int kf_latent_attention(kf_ctx* ctx, float* lat_out, float* qa_work, const float* q, int ldq, const void* w_uk_bf16, const void* sink_bf16,
                                    const void* cache, int cache_f32, size_t slot_stride, const double* inv_freq_dev, const int32_t* pos_dev,
                                    const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale, int max_pos_hint) {
-    if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !sink_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
-    KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0, "rank + rot_dim <= 640");
+    if (!sink_bf16) return KF_ERR_BAD_ARG;
+    return kf_latent_attention_ex(ctx, lat_out, qa_work, q, ldq, w_uk_bf16, sink_bf16, cache, cache_f32, slot_stride, inv_freq_dev, pos_dev, slot_dev, M, H, dn,
+                                  rot_dim, rot_dims, rank, scale, max_pos_hint, 0, 1.f);
+}
+// the same with an optional sink (NULL: a plain softmax over the keys), the pair layout of the rotation and the factor on cosine and sine
+// as in kf_latent_append_ex
+extern "C" int kf_latent_attention_ex(kf_ctx* ctx, float* lat_out, float* qa_work, const float* q, int ldq, const void* w_uk_bf16, const void* sink_bf16,
+                                      const void* cache, int cache_f32, size_t slot_stride, const double* inv_freq_dev, const int32_t* pos_dev,
+                                      const int32_t* slot_dev, int M, int H, int dn, int rot_dim, int rot_dims, int rank, float scale, int max_pos_hint,
+                                      int layout, float amp) {
+    if (!ctx || !lat_out || !qa_work || !q || !w_uk_bf16 || !cache || !inv_freq_dev || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, M >= 1 && H >= 1 && dn >= 1 && rank >= 1 && rank + rot_dim <= 32 * LMAX && rot_dims <= rot_dim && rot_dims % 2 == 0 &&
+                        (layout == 0 || layout == 1), "rank + rot_dim <= 640");
     dim3 grid(M, H), qgrid((M + QT - 1) / QT, H, (rank + 127) / 128);
     kf_latent_query_kernel<<<qgrid, 128, (size_t)QT * (dn + rot_dim) * 4, ctx->stream>>>(qa_work, q, ldq, (const uint16_t*)w_uk_bf16, inv_freq_dev, pos_dev, M,
-                                                                                       H, dn, rot_dim, rot_dims, rank, scale);
+                                                                                       H, dn, rot_dim, rot_dims, rank, scale, layout, amp);
     KF_LAUNCH_CHECK(ctx);
     if (!cache_f32 && rank % 8 == 0 && (rank + rot_dim) % 8 == 0 && rank <= NTW * 32 && rank + rot_dim <= KSW * 64 && (slot_stride * 2) % 16 == 0 &&
         ((uintptr_t)cache & 15) == 0) {

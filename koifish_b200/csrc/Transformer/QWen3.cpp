@@ -87,7 +87,7 @@ MODEL_CARD MODEL_CARD::FromJSON(const JSON& j0) {
     if (const JSON* s = j0.path({"init", "norm_sigma"})) c.norm_sigma = (float)s->as_double(c.norm_sigma);
     std::string a = c.arch;
     std::transform(a.begin(), a.end(), a.begin(), ::toupper);
-    if (!FindArch(a)) throw std::runtime_error("model.arch '" + c.arch + "' is outside the hot path (registered: QWEN3, SIPAZEN, KIVORAX, SEDOTAR)");
+    if (!FindArch(a)) throw std::runtime_error("model.arch '" + c.arch + "' is outside the hot path (registered: QWEN3, SIPAZEN, KIVORAX, SEDOTAR, FAZOLORN)");
     if (const JSON* s = j0.path({"gpt", "compute_dtype"})) c.compute_f32 = s->as_string("") == "float32";
     c.logit_rows_cfg = jint(j0, {"gpt", "logit_rows"}, c.logit_rows_cfg);
     if (c.max_seq_len <= 0 || c.max_batch <= 0) throw std::runtime_error("gpt.max_seq_len / gpt.max_batch must be positive");
@@ -108,7 +108,7 @@ const ARCH_ENTRY* FindArch(const std::string& name) {
     static const ARCH_ENTRY qwen3 = {"QWEN3", nullptr, BuildQwen3, ForwardQwen3, nullptr};
     std::string a = name;
     std::transform(a.begin(), a.end(), a.begin(), ::toupper);
-    const ARCH_ENTRY* all[] = {&qwen3, SipazenArch(), KivoraxArch(), SedotarArch()};
+    const ARCH_ENTRY* all[] = {&qwen3, SipazenArch(), KivoraxArch(), SedotarArch(), FazolornArch()};
     for (const ARCH_ENTRY* e : all)
         if (a == e->name) return e;
     return nullptr;

@@ -21,7 +21,8 @@ namespace koifish {
 // One layer of a hybrid stack (config "layers": [{"type", "mixer": {...}, "mlp": {...} | null}, ...]): which sequence mixer it has, with
 // that mixer's sizes, and its feed-forward.  Layers of one model may differ in every size.
 struct MIXER_CARD {
-    std::string type;  // "mamba2" (state-space) | "latent_attention" | "channel_delta" | "gla" | "parallel" (attention beside a gated LRU)
+    std::string type;  // "mamba2" (state-space) | "latent_attention" | "channel_delta" | "gla" | "parallel" (attention beside a gated LRU) |
+                       // "mingru" (channel-wise gated recurrence) | "attention" (sigmoid-weighted, inside blocks of positions)
     // state-space mixer: heads x vdim inner channels, state rows per head, B/C groups, gated-norm groups, convolution taps
     int heads = 0, vdim = 0, state = 0, groups = 1, norm_groups = 1, conv = 1;
     // latent attention: per head `dim` plain + `rot_dim` rotated query/key entries, values of vdim, latent rank; rotation on the first
@@ -44,6 +45,12 @@ struct MIXER_CARD {
     float softcap = 0.f;
     bool sink = false;
     double yarn_factor = 0.0, yarn_original = 0.0, yarn_fast = 0.0, yarn_slow = 0.0;
+    // latent attention whose queries pass a latent of q_rank entries (RMS-normed) before their up-projection (0: projected directly)
+    int q_rank = 0;
+    // sigmoid-weighted attention: a query sees the keys of its own block of `block` consecutive positions, counted from position 0 (0: all)
+    int block = 0;
+    // channel-wise gated recurrence (minGRU): channels of the state
+    int width = 0;
     // two mixers side by side that read the same input (Sedotar's "parallel"): this card is the left one, `right` the other; the result is
     // left_scale * left + right_scale * right
     std::shared_ptr<MIXER_CARD> right;
@@ -54,6 +61,12 @@ struct MOE_CARD {
     bool dense   = false;  // one feed-forward of width ff with biases instead of routed experts
     int experts = 0, top = 0, ff = 0;
     int shared_ff = 0;  // 0: no shared expert
+    float limit = 0.f;  // dense, clamped form: gate <= limit, |up| <= limit (0: the feed-forward is not of that form)
+    // routing from sigmoid scores: selection over score + a learned correction inside the `keep` best of `groups` groups of neighbouring
+    // experts, weights route_scale * score, not renormalised (sigmoid_route false: softmax routing)
+    bool sigmoid_route = false;
+    int groups = 1, keep = 1;
+    float route_scale = 1.f;
 };
 struct LAYER_CARD {
     MIXER_CARD mixer;
@@ -84,6 +97,9 @@ struct MODEL_CARD {
     int logit_rows_cfg  = 0;      // gpt.logit_rows: rows of the logits buffers (default max(64, max_batch))
     float embed_scale   = 1.f;    // the embedding row is multiplied by this
     int side_dim        = 0;      // per-layer token input: entries of the side embedding that each layer reads (0: none)
+    // layers loop_start .. loop_stop - 1 run loop_times times in a row on the same weights, each pass with a cache / state of its own
+    int loop_start = 0, loop_stop = 0, loop_times = 1;
+    float logit_scale = 1.f;      // the head's result is multiplied by this
     bool IsHybrid() const { return !layers.empty(); }
 
     // accepts a Koifish JSON (cases/qwen3/*.json layout) or an HF config.json, optionally wrapped as {"hf_config": {...}}
@@ -198,6 +214,7 @@ const ARCH_ENTRY* FindArch(const std::string& name);
 const ARCH_ENTRY* SipazenArch();  // Sipazen.cpp
 const ARCH_ENTRY* KivoraxArch();  // Kivorax.cpp
 const ARCH_ENTRY* SedotarArch();  // Sedotar.cpp
+const ARCH_ENTRY* FazolornArch(); // Fazolorn.cpp
 
 // ---- the model ------------------------------------------------------------------------------------------------------------
 struct Fish {

@@ -333,31 +333,44 @@ int SSMixer::cuInfer(int M, const float* u, int ldu, int off_in) {
     return KF_OK;
 }
 
-int LatentAttention::cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g) {
+int LatentAttention::cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g, int cache_layer) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
     const MIXER_CARD& m = card;
     const int ak = f.config.compute_f32 ? 1 : 0;
-    SeqStateCache::Layer& sl = f.states.layers[layer];
-    const int W = m.kv_rank + m.rot_dim;
-    (void)W;
-    KF_TRY(kf_latent_append(f.ctx, sl.rows, ak, sl.row_stride, u + off_dkv, ldu, dkv_norm->data, inv_freq, f.d_pos, f.d_slot, M, m.kv_rank, m.rot_dim, m.rot_dims,
-                            f.config.norm_rms_eps));
-    KF_TRY(kf_latent_attention(f.ctx, s.lat, s.y, u + off_q, ldu, uk->data, sink->data, sl.rows, ak, sl.row_stride, inv_freq, f.d_pos, f.d_slot, M, m.heads,
-                               m.dim, m.rot_dim, m.rot_dims, m.kv_rank, m.scale, f.attn_hint));
-    KF_TRY(kf_latent_expand(f.ctx, s.act, ak, s.lat, uv->data, u + off_g, ldu, M, m.heads, m.vdim, m.kv_rank));
+    SeqStateCache::Layer& sl = f.states.layers[cache_layer < 0 ? layer : cache_layer];
+    const float* qv = u + off_q;
+    int ldq = ldu;
+    if (dq) {  // queries through their latent: RMS norm of the down-projection, then the up-projection
+        const int nq = m.heads * (m.dim + m.rot_dim);
+        KF_TRY(kf_group_rmsnorm(f.ctx, s.mid, ak, m.q_rank, nullptr, 0.f, u + off_q, ldu, nullptr, 0, nullptr, 0, dq_norm->data, nullptr, M, m.q_rank, 1,
+                                f.config.norm_rms_eps));
+        kf_tensor_desc d = uq->Desc();
+        KF_TRY(kf_linear_g(f.ctx, s.v, nq, &d, s.mid, ak, m.q_rank, M));
+        qv = s.v, ldq = nq;
+    }
+    KF_TRY(kf_latent_append_ex(f.ctx, sl.rows, ak, sl.row_stride, u + off_dkv, ldu, dkv_norm->data, inv_freq, f.d_pos, f.d_slot, M, m.kv_rank, m.rot_dim,
+                               m.rot_dims, f.config.norm_rms_eps, layout, amp));
+    KF_TRY(kf_latent_attention_ex(f.ctx, s.lat, s.y, qv, ldq, uk->data, sink ? sink->data : nullptr, sl.rows, ak, sl.row_stride, inv_freq, f.d_pos, f.d_slot, M,
+                                  m.heads, m.dim, m.rot_dim, m.rot_dims, m.kv_rank, m.scale, f.attn_hint, layout, amp));
+    KF_TRY(kf_latent_expand(f.ctx, s.act, ak, s.lat, uv->data, off_g >= 0 ? u + off_g : nullptr, ldu, M, m.heads, m.vdim, m.kv_rank));
     KF_TRY(Lin(f, s.sub, o, s.act, M));
     return KF_OK;
 }
 
-int MoE::cuInfer(int M, const float* u, int ldu, int off_router, int off_sg) {
+int MoE::cuInfer(int M, const float* u, int ldu, int off_router, int off_sg, float* into_residual) {
     Fish& f = *hFish;
     std::string* hFishErr = &f.error;
     HybridScratch& s = *f.hscratch;
     const int E = f.config.n_embd, X = card.experts, top = card.top;
     const int ak = f.config.compute_f32 ? 1 : 0;
-    KF_TRY(kf_moe_route(f.ctx, s.idx, s.wgt, s.offsets, s.entry_slot, s.slot_row, s.slot_group, s.work, u + off_router, ldu, router_b->data, M, X, top));
+    const void* rb = router_b ? router_b->data : nullptr;
+    if (card.sigmoid_route)
+        KF_TRY(kf_moe_route_grouped(f.ctx, s.idx, s.wgt, s.offsets, s.entry_slot, s.slot_row, s.slot_group, s.work, u + off_router, ldu, rb, M, X, top, card.groups,
+                                    card.keep, card.route_scale));
+    else
+        KF_TRY(kf_moe_route(f.ctx, s.idx, s.wgt, s.offsets, s.entry_slot, s.slot_row, s.slot_group, s.work, u + off_router, ldu, rb, M, X, top));
     const void* const* tb = (const void* const*)tables;
     KF_TRY(kf_linear_grouped(f.ctx, s.h1, card.ff, tb, tb + X, X, card.ff, E, s.hact, ak, E, s.offsets, s.slot_group, s.slot_row, M * top));
     KF_TRY(kf_linear_grouped(f.ctx, s.yslots, E, tb + 2 * X, nullptr, X, E, card.ff, s.h1, ak, card.ff, s.offsets, s.slot_group, nullptr, M * top));
@@ -367,7 +380,8 @@ int MoE::cuInfer(int M, const float* u, int ldu, int off_router, int off_sg) {
         KF_TRY(kf_linear_g_swiglu(f.ctx, s.hs, card.shared_ff, &dg, &du, s.hact, ak, E, M));
         KF_TRY(Lin(f, s.shared, sh_down, s.hs, M));
     }
-    KF_TRY(kf_moe_combine(f.ctx, s.sub, s.yslots, s.entry_slot, s.wgt, sh ? s.shared : nullptr, sh ? u + off_sg : nullptr, ldu, M, E, top));
+    KF_TRY(kf_moe_combine_ex(f.ctx, into_residual ? into_residual : s.sub, s.yslots, s.entry_slot, s.wgt, sh ? s.shared : nullptr, sh ? u + off_sg : nullptr, ldu,
+                             M, E, top, into_residual ? 1 : 0));
     return KF_OK;
 }
 

@@ -55,18 +55,24 @@ struct SSMixer : GeNeuron {
 struct LatentAttention : GeNeuron {
     MIXER_CARD card;
     int layer = 0;
-    hGTensor q, dkv, dkv_norm, uk, uv, sink, g, o;
+    hGTensor q, dkv, dkv_norm, uk, uv, sink, g, o;  // sink, g may be absent: plain softmax, no output gate
+    hGTensor dq, dq_norm, uq;    // queries through a latent (card.q_rank > 0): q = uq . rmsnorm(dq h); then `q` is absent
     double* inv_freq = nullptr;  // device [rot_dims / 2]
-    int cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g);
+    int layout = 0;              // rotation pairs: 0 (i, i + dims/2), 1 (2i, 2i + 1)
+    float amp = 1.f;             // multiplies cosine and sine
+    // u: the stacked first projections; off_q: the query projection (or, with a query latent, its down-projection); off_g < 0: no gate;
+    // cache_layer: which entry of the model's SeqStateCache holds this run's rows (-1: `layer`)
+    int cuInfer(int M, const float* u, int ldu, int off_q, int off_dkv, int off_g, int cache_layer = -1);
 };
 struct MoE : GeNeuron {
     MOE_CARD card;
-    hGTensor router, router_b;
+    hGTensor router, router_b;  // router_b: bias of the softmax routing, or the selection correction of the sigmoid routing
     std::vector<hGTensor> gate, up, down;
     hGTensor sh_gate, sh_up, sh_down, sh_sg;
     void** tables = nullptr;  // device: [3][experts] weight pointers (gate | up | down)
     int Prepare();
-    int cuInfer(int M, const float* u, int ldu, int off_router, int off_sg);
+    // into_residual: the weighted sum of the experts is added to that buffer instead of being written to the sublayer result
+    int cuInfer(int M, const float* u, int ldu, int off_router, int off_sg, float* into_residual = nullptr);
 };
 struct HybridBlock : GeNeuron {
     int layer = 0;
