@@ -402,6 +402,10 @@ int kf_qk_prepare_ex(kf_ctx* ctx, float* x_dev, int ldx, int nq, int nk, int nv,
 int kf_attn_sigmoid(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float* q_dev, int ldq, const void* cache_dev, int cache_f32, size_t slot_stride,
                     int ring, const void* head_bias_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int H, int G, int dk, int dv, float scale,
                     int block, int window, int max_keys_hint, float out_scale);
+/* the same attention for a panel of M consecutive tokens of one slot on the tensor cores (bf16 ring cache, dk == dv in {64, 128}; attention.cu) */
+int kf_attn_sigmoid_prefill(kf_ctx* ctx, void* out_bf16_dev, int ldo, const void* q_bf16_dev, const void* cache_dev, size_t slot_stride, int ring,
+                            const void* head_bias_bf16_dev, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd, float scale,
+                            int block, float out_scale);
 /* kf_latent_append / kf_latent_attention with the rotation's pair layout (0: (i, i + dims/2); 1: (2i, 2i+1)), a factor on cosine and sine, and an
  * optional sink (NULL: plain softmax) */
 int kf_latent_append_ex(kf_ctx* ctx, void* cache_dev, int cache_f32, size_t slot_stride, const float* ckr_dev, int ldc, const void* norm_w_bf16_dev,

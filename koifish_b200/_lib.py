@@ -133,6 +133,16 @@ SIGNATURES = {
     "kf_attn_window": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _F]),
     "kf_attn_window_prefill": (_I, [_P, _P, _I, _P, _P, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _F, _F, _I, _F]),
     "kf_d2d_2d": (_I, [_P, _P, _SZ, _P, _SZ, _SZ, _SZ]),
+    "kf_residual_prenorm": (_I, [_P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _F]),
+    "kf_glu_clamped": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _F, _F, _F]),
+    "kf_scale_f32": (_I, [_P, _P, _SZ, _F]),
+    "kf_moe_route_grouped": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F]),
+    "kf_mingru": (_I, [_P, _P, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _P, _SZ, _P, _P, _I, _I, _I]),
+    "kf_qk_prepare_ex": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _F, _I, _P, _F, _I, _P, _I, _SZ, _I, _P, _P, _P, _I]),
+    "kf_attn_sigmoid": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F]),
+    "kf_attn_sigmoid_prefill": (_I, [_P, _P, _I, _P, _P, _SZ, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _F]),
+    "kf_latent_append_ex": (_I, [_P, _P, _I, _SZ, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _F]),
+    "kf_latent_attention_ex": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _SZ, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _F]),
     "kf_nccl_unique_id": (_I, [_P]),
     "kf_ctx_init_nccl": (_I, [_P, _P, _I, _I]),
     "kf_allreduce_bf16": (_I, [_P, _P, _SZ]),

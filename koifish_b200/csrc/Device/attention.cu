@@ -559,17 +559,23 @@ struct PfBias {
     int ring, window;
     float softcap;
     const uint16_t* sink;
-    int out_ld;       // MODE 2: elements between the output rows of consecutive tokens
-    float out_scale;  // MODE 2: factor on the result before it is rounded
+    int out_ld;       // MODE 2, 3: elements between the output rows of consecutive tokens
+    float out_scale;  // MODE 2, 3: factor on the result before it is rounded
+    // MODE 3 (sigmoid weights inside blocks of positions): a query at p sees the positions t <= p of its own block of `block` positions,
+    // counted from position 0 (0x7fffffff: one block); the weight of a key is sigmoid(scale q.k + hbias[h]) (bf16 [n_head] or NULL); the
+    // weights are not normalised over the keys
+    int block;
+    const uint16_t* hbias;
 };
 // MODE 0: Qwen3's plain causal attention over separate K and V caches.  MODE 1: see above.  MODE 2: the side-by-side rows and hi + lo
-// softmax weights of MODE 1 without penalty and gate, with the window, cap, sink and ring of PfBias.
+// softmax weights of MODE 1 without penalty and gate, with the window, cap, sink and ring of PfBias.  MODE 3: the rows and the ring of
+// MODE 2 with sigmoid weights inside blocks of positions -- no running maximum, no rescaling, no denominator.
 template <int HD, int BKV, int MODE>
 __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ q,
                                                               const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                                                               const int32_t* __restrict__ pos_dev, int M, int n_head, int n_kv, int max_seq,
                                                               float sqrt_hd, PfBias xb) {
-    constexpr bool BIAS = MODE == 1, WIN = MODE == 2, ROWS = MODE != 0;
+    constexpr bool BIAS = MODE == 1, WIN = MODE == 2, SIG = MODE == 3, RING = MODE >= 2, ROWS = MODE != 0;
     constexpr int CH = HD / 8;  // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t pf_smem[];
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(pf_smem);
@@ -584,7 +590,12 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
     const int q0 = qt * kPfQ;
     const int kv_len = pos0 + min(M, q0 + kPfQ);  // rows visible to the last query row of this tile
     const int ntiles = (kv_len + BKV - 1) / BKV;
-    const int kt0 = WIN ? max(0, pos0 + q0 - xb.window + 1) / BKV : 0;  // the first tile that the tile's first query still sees
+    // the first tile that the tile's first query still sees
+    const int kt0 = WIN ? max(0, pos0 + q0 - xb.window + 1) / BKV : SIG ? (((pos0 + q0) / xb.block) * xb.block) / BKV : 0;
+    const float hb2 = (SIG && xb.hbias) ? bf16_bits_to_f32(xb.hbias[h]) * 1.4426950408889634f : 0.f;
+    // where the blocks of this thread's two query rows start
+    const int b_lo = SIG ? ((pos0 + q0 + (threadIdx.x >> 5) * 16 + ((threadIdx.x & 31) >> 2)) / xb.block) * xb.block : 0;
+    const int b_hi = SIG ? ((pos0 + q0 + (threadIdx.x >> 5) * 16 + ((threadIdx.x & 31) >> 2) + 8) / xb.block) * xb.block : 0;
     auto sw = [](int row, int c) { return (uint32_t)((row * CH + (c ^ (row & 7))) * 16); };
 
     // ---- Q tile + first K / V tile ----
@@ -597,7 +608,7 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
         for (int i = tid; i < BKV * CH; i += 128) {
             const int r = i / CH, c = i % CH;
             // rows past kv_len are masked below; keep the address inside the cache (WIN: any row of the ring will do for those)
-            const int t = WIN ? (kt * BKV + r) % xb.ring : min(kt * BKV + r, max_seq - 1);
+            const int t = RING ? (kt * BKV + r) % xb.ring : min(kt * BKV + r, max_seq - 1);
             cp16(sK + buf * (BKV * HD * 2) + sw(r, c), kc + (size_t)t * kv_dim + (size_t)kvh * HD + c * 8, true);
             cp16(sV + buf * (BKV * HD * 2) + sw(r, c), vc + (size_t)t * kv_dim + (size_t)kvh * HD + c * 8, true);
         }
@@ -651,6 +662,10 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
                 if (BIAS) {
                     const int dist = ((e & 2) ? p_hi : p_lo) - (kt * BKV + j * 8 + 2 * t4 + (e & 1));
                     v = dist < 0 ? -INFINITY : fmaf(v, SCB, -pen1 * __log2f(fmaf(pen2, (float)dist, 1.f)));
+                } else if (SIG) {
+                    // sigmoid(s + b) = 1 / (1 + 2^-(s + b) log2 e); a key outside the query's block or after it weighs nothing
+                    const int tcol = kt * BKV + j * 8 + 2 * t4 + (e & 1);
+                    v = (tcol > ((e & 2) ? p_hi : p_lo) || tcol < ((e & 2) ? b_hi : b_lo)) ? 0.f : __fdividef(1.f, 1.f + exp2f(-fmaf(v, SCB, hb2)));
                 } else if (WIN) {
                     const int dist = ((e & 2) ? p_hi : p_lo) - (kt * BKV + j * 8 + 2 * t4 + (e & 1));
                     // cap * tanh(s / cap) = cap * (1 - 2 / (e^{2 s / cap} + 1)), brought to the log2 domain
@@ -666,18 +681,21 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
             mx_lo = fmaxf(mx_lo, fmaxf(sc[j][0], sc[j][1]));
             mx_hi = fmaxf(mx_hi, fmaxf(sc[j][2], sc[j][3]));
         }
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)), mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)), mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        if (!SIG) {
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)), mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)), mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        }
         const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
         const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;  // fully masked row so far
-        const float c_lo = exp2f((m_lo - base_lo) * SC), c_hi = exp2f((m_hi - base_hi) * SC);
+        const float c_lo = SIG ? 1.f : exp2f((m_lo - base_lo) * SC), c_hi = SIG ? 1.f : exp2f((m_hi - base_hi) * SC);
         m_lo = mn_lo, m_hi = mn_hi;
         float rs_lo = 0.f, rs_hi = 0.f;
         uint32_t pa[BKV / 16][4], pb[ROWS ? BKV / 16 : 1][4];
 #pragma unroll
         for (int j = 0; j < BKV / 8; j++) {
-            const float p0 = exp2f((sc[j][0] - base_lo) * SC), p1 = exp2f((sc[j][1] - base_lo) * SC);
-            const float p2 = exp2f((sc[j][2] - base_hi) * SC), p3 = exp2f((sc[j][3] - base_hi) * SC);
+            // SIG: sc already holds the weights themselves
+            const float p0 = SIG ? sc[j][0] : exp2f((sc[j][0] - base_lo) * SC), p1 = SIG ? sc[j][1] : exp2f((sc[j][1] - base_lo) * SC);
+            const float p2 = SIG ? sc[j][2] : exp2f((sc[j][2] - base_hi) * SC), p3 = SIG ? sc[j][3] : exp2f((sc[j][3] - base_hi) * SC);
             rs_lo += p0 + p1, rs_hi += p2 + p3;
             const uint32_t w01 = pack_bf16x2(p0, p1), w23 = pack_bf16x2(p2, p3);
             pa[j >> 1][(j & 1) * 2 + 0] = w01;  // A fragment of P for the 16 tokens of n-tiles (2i, 2i+1)
@@ -688,8 +706,10 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
             }
         }
         l_lo = l_lo * c_lo + rs_lo, l_hi = l_hi * c_hi + rs_hi;
+        if (!SIG) {
 #pragma unroll
-        for (int j = 0; j < HD / 8; j++) o[j][0] *= c_lo, o[j][1] *= c_lo, o[j][2] *= c_hi, o[j][3] *= c_hi;
+            for (int j = 0; j < HD / 8; j++) o[j][0] *= c_lo, o[j][1] *= c_lo, o[j][2] *= c_hi, o[j][3] *= c_hi;
+        }
         // ---- O += P V ----
 #pragma unroll
         for (int kc_ = 0; kc_ < BKV / 16; kc_++) {
@@ -718,8 +738,8 @@ __global__ void __launch_bounds__(128, KF_PF_MINB) kf_attn_prefill_kernel(uint16
 #pragma unroll
         for (int j = 0; j < HD / 8; j++) o[j][0] *= c_lo, o[j][1] *= c_lo, o[j][2] *= c_hi, o[j][3] *= c_hi;
     }
-    const float i_lo = (WIN ? xb.out_scale : 1.f) / l_lo, i_hi = (WIN ? xb.out_scale : 1.f) / l_hi;
-    const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8, o_dim = WIN ? xb.out_ld : q_dim;
+    const float i_lo = SIG ? xb.out_scale : (WIN ? xb.out_scale : 1.f) / l_lo, i_hi = SIG ? xb.out_scale : (WIN ? xb.out_scale : 1.f) / l_hi;
+    const int r_lo = q0 + warp * 16 + g, r_hi = r_lo + 8, o_dim = RING ? xb.out_ld : q_dim;
 #pragma unroll
     for (int j = 0; j < HD / 8; j++) {
         const int d = j * 8 + 2 * t4;
@@ -1121,6 +1141,43 @@ extern "C" int kf_attn_window_prefill(kf_ctx* ctx, void* out, int ldo, const voi
             set[ctx->device] = true;
         }
         kf_attn_prefill_kernel<64, KF_PF_BKV, 2><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv, ring,
+                                                                                 1.f, xb);
+    }
+    KF_LAUNCH_CHECK(ctx);
+    return KF_OK;
+}
+
+// Sigmoid-weighted attention inside blocks of positions (kf_attn_sigmoid of attn_window.cu on the tensor cores) for a panel of M consecutive
+// tokens of one slot: q_bf16 [M][n_head * hd] finished queries; cache rows [slot][ring][n_kv * hd keys | n_kv * hd values] (bf16), position
+// t in row t % ring; out [M][ldo] bf16 = out_scale * sum_t sigmoid(scale q.k_t + head_bias[h]) v_t over the positions t <= p of p's block
+// of `block` positions (block <= 0: all earlier positions).  The ring must cover a block (every position when there are no blocks).
+extern "C" int kf_attn_sigmoid_prefill(kf_ctx* ctx, void* out, int ldo, const void* q_bf16, const void* cache, size_t slot_stride, int ring,
+                                       const void* head_bias_bf16, const int32_t* pos_dev, const int32_t* slot_dev, int M, int n_head, int n_kv, int hd,
+                                       float scale, int block, float out_scale) {
+    if (!ctx || !out || !q_bf16 || !cache || !pos_dev || !slot_dev) return KF_ERR_BAD_ARG;
+    KF_REQUIRE(ctx, (hd == 128 || hd == 64) && n_head % n_kv == 0 && M >= 1 && ring >= 1 && (block <= 0 || ring >= block) && ldo >= n_head * hd && ldo % 2 == 0,
+               "head size 64/128, GQA, ring");
+    const size_t smem = (size_t)(kPfQ + 4 * KF_PF_BKV) * hd * 2;
+    dim3 grid((M + kPfQ - 1) / kPfQ, n_head);
+    PfBias xb = {nullptr, nullptr, nullptr, 0, slot_dev, slot_stride, 2 * n_kv * hd, scale, ring, 0x7fffffff, 0.f, nullptr, ldo, out_scale,
+                 block > 0 ? block : 0x7fffffff, (const uint16_t*)head_bias_bf16};
+    const uint16_t* kc = (const uint16_t*)cache;
+    const uint16_t* vc = kc + (size_t)n_kv * hd;
+    if (hd == 128) {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<128, KF_PF_BKV, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<128, KF_PF_BKV, 3><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv, ring,
+                                                                                  1.f, xb);
+    } else {
+        static bool set[kf_ctx::kMaxDevices] = {};
+        if (!set[ctx->device]) {
+            KF_CUDA(ctx, cudaFuncSetAttribute(kf_attn_prefill_kernel<64, KF_PF_BKV, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set[ctx->device] = true;
+        }
+        kf_attn_prefill_kernel<64, KF_PF_BKV, 3><<<grid, 128, smem, ctx->stream>>>((uint16_t*)out, (const uint16_t*)q_bf16, kc, vc, pos_dev, M, n_head, n_kv, ring,
                                                                                  1.f, xb);
     }
     KF_LAUNCH_CHECK(ctx);

@@ -234,7 +234,7 @@ static int BuildFazolorn(Fish& f) {
                 KF_TRY(kf_ctx_sync(f.ctx));  // fr leaves scope
             }
             blk->cat.Plan({a->q, a->k});
-            maxA = std::max<size_t>(maxA, nq);
+            maxA = std::max<size_t>(maxA, nq), maxY = std::max<size_t>(maxY, nq / 2 + 1);  // maxY: the bf16 query of the panel kernel
             blk->attn = std::move(a);
         } else {
             auto a = std::make_unique<LatentAttention>();
@@ -400,10 +400,16 @@ int BlockAttention::cuInfer(int M, float* u, int ldu, int off, int cache) {
     // a block longer than the ring means the ring was cut to max_seq rows: every position lies in block 0 and none is ever masked
     const int blk = m.block <= sl.ring ? m.block : 0;
     // biases, rotation of q (in place) and k; the row [rotated k | k as projected] joins the ring: the values are the unrotated keys
+    // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, other sizes, 32-bit) to the general kernel
+    const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && (m.dim == 64 || m.dim == 128);
     KF_TRY(kf_qk_prepare_ex(f.ctx, u + off, ldu, nq, nk, nk, m.dim, q_b->data, k_b->data, 1, nullptr, nullptr, c.norm_rms_eps, m.rot_dims, inv_freq, amp, 1, sl.rows,
-                            ak, sl.row_stride, sl.ring, nullptr, f.d_pos, f.d_slot, M));
-    KF_TRY(kf_attn_sigmoid(f.ctx, s.act, ak, nq, u + off, ldu, sl.rows, ak, sl.row_stride, sl.ring, pb->data, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim,
-                           m.dim, m.scale, blk, 0, f.attn_hint + 1, 1.f));
+                            ak, sl.row_stride, sl.ring, tile ? s.y : nullptr, f.d_pos, f.d_slot, M));
+    if (tile)
+        KF_TRY(kf_attn_sigmoid_prefill(f.ctx, s.act, nq, s.y, sl.rows, sl.row_stride, sl.ring, pb->data, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim, m.scale,
+                                       blk, 1.f));
+    else
+        KF_TRY(kf_attn_sigmoid(f.ctx, s.act, ak, nq, u + off, ldu, sl.rows, ak, sl.row_stride, sl.ring, pb->data, f.d_pos, f.d_slot, M, m.heads, m.kv_heads, m.dim,
+                               m.dim, m.scale, blk, 0, f.attn_hint + 1, 1.f));
     KF_TRY(Lin(f, s.sub, c.n_embd, o, s.act, nq, M));
     return KF_OK;
 }

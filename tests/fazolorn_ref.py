@@ -135,8 +135,9 @@ def dense_ff(h, f, W, p):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].to(D).T
 
 
-def route(h, f, W, p):
-    """per token: (chosen experts, their weights)"""
+def route(h, f, W, p, margins=None):
+    """per token: (chosen experts, their weights); margins (a list) receives, per token, the smallest gap that decided anything -- between
+    the last kept and the first dropped group, between the last chosen and the first rejected expert"""
     r = f["router"]
     X, top = r["experts"], r["top"]
     gr = r.get("groups") or {"count": 1, "keep": 1}
@@ -151,14 +152,21 @@ def route(h, f, W, p):
         for g in range(gr["count"]):
             if g not in kept:
                 ch[g * per:(g + 1) * per] = -math.inf
-        idx = sorted(range(X), key=lambda e: (-ch[e].item(), e))[:top]
+        order = sorted(range(X), key=lambda e: (-ch[e].item(), e))
+        idx = order[:top]
         picks.append((idx, [s[t, e] * r["scale"] for e in idx]))
+        if margins is not None:
+            by_score = sorted(score, reverse=True)
+            gap = by_score[gr["keep"] - 1] - by_score[gr["keep"]] if gr["keep"] < gr["count"] else math.inf
+            if top < X and ch[order[top]] > -math.inf:
+                gap = min(gap, (ch[order[top - 1]] - ch[order[top]]).item())
+            margins.append(gap)
     return picks
 
 
-def experts_ff(h, f, W, p):
+def experts_ff(h, f, W, p, margins=None):
     out = torch.zeros_like(h)
-    for t, (idx, wgt) in enumerate(route(h, f, W, p)):
+    for t, (idx, wgt) in enumerate(route(h, f, W, p, margins)):
         for e, w in zip(idx, wgt):
             q = "%se%d." % (p, e)
             y = silu(lin(W, q + "gate", h[t])) * lin(W, q + "up", h[t])
@@ -178,8 +186,9 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(lp["stop"], L)]
 
 
-def forward(cfg, W, tokens, trace=None):
-    """logits [T, vocab] of one sequence from position 0; trace (a list) receives x after every layer run"""
+def forward(cfg, W, tokens, trace=None, margins=None):
+    """logits [T, vocab] of one sequence from position 0; trace (a list) receives x after every layer run; margins (a list) one list of
+    per-token routing gaps for every run of a layer with experts"""
     eps = cfg["norm"]["eps"]
     x0 = W["embed"].to(D)[torch.tensor(tokens)]
     x = x0.clone()
@@ -201,7 +210,13 @@ def forward(cfg, W, tokens, trace=None):
         f = ly.get("mlp")
         if f:
             h = rmsnorm(x, W[p + "norm2"], eps)
-            x = x + (dense_ff(h, f, W, p + "mlp.") if f["kind"] == "dense" else experts_ff(h, f, W, p + "mlp."))
+            if f["kind"] == "dense":
+                x = x + dense_ff(h, f, W, p + "mlp.")
+            else:
+                gaps = [] if margins is not None else None
+                x = x + experts_ff(h, f, W, p + "mlp.", gaps)
+                if margins is not None:
+                    margins.append(gaps)
         if trace is not None:
             trace.append(x.clone())
     return rmsnorm(x, W["final.norm"], eps) @ W["head"].to(D).T * cfg.get("logit_scale", 1.0)

@@ -1,0 +1,478 @@
+"""GPU tests of the Fazolorn stack against the plain float64 restatement in fazolorn_ref.py, on small random models made here.
+
+Gates: with gpt.compute_dtype = float32 the logits agree to 2e-4 (rms of the difference, mean removed, over the rms of the logits);
+in bf16 nine rows in ten to 6e-2.  Weights are drawn on the bf16 grid, so both sides hold the same numbers.  Where random weights would
+hide a fault they are shaped: query projections scaled up so that the sigmoid weights sit near 0 or 1 and the softmax is peaked (a block
+edge one position off, a key of the wrong ring row, a far key lost then moves the logits far), head biases shifted so that leaving them
+out shows, update gates nearly closed so that the first tokens still matter hundreds of steps later.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import koifish_b200 as kf
+import fazolorn_ref as ref
+from fazolorn_models import attn, bf16_grid, bits, config, dense, gru, latent, layer, moe, tokens, weights
+from st_util import write_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {True: 2e-4, False: 6e-2}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = kf.Context(0)
+    yield c
+    c.close()
+
+
+def build(ctx, cfg, W, f32, max_seq=256, slots=2, panel=64, logit_rows=None):
+    gpt = {"max_seq_len": max_seq, "max_batch": slots, "max_prefill": panel, "logit_rows": logit_rows or panel}
+    if f32:
+        gpt["compute_dtype"] = "float32"
+    m = kf.Model(ctx, {"hf_config": cfg, "gpt": gpt})
+    assert sorted(m.tensor_names()) == sorted(W.keys())
+    for k, v in W.items():
+        m.set_tensor(k, bits(v).reshape(-1, v.shape[-1]) if v.dim() > 1 else bits(v))
+    return m
+
+
+def rel(got, want, q=1.0):
+    """largest (q = 1) or q-quantile row error: rms of the difference, mean removed, over the rms of the wanted logits"""
+    d = np.asarray(got, dtype=np.float64) - np.asarray(want, dtype=np.float64)
+    d = d - d.mean(-1, keepdims=True)
+    w = np.asarray(want, dtype=np.float64)
+    w = w - w.mean(-1, keepdims=True)
+    return float(np.quantile(np.atleast_1d(np.sqrt((d ** 2).mean(-1))), q) / np.sqrt((w ** 2).mean()))
+
+
+def close(got, want, f32):
+    if f32:
+        return rel(got, want) < TOL[True]
+    return rel(got, want, 0.9) < TOL[False] and rel(got, want) < 0.5
+
+
+def oracle(cfg, W, toks):
+    return ref.forward(cfg, W, list(toks)).numpy()
+
+
+def settled(cfg, W, toks, gap=0.02):
+    """the positions whose own choice of experts is no close call in the oracle: in bf16 a near tie between two experts may legitimately go
+    the other way, so rows that rest on one are not compared (32-bit runs compare every row)"""
+    margins = []
+    ref.forward(cfg, W, list(toks), margins=margins)
+    return np.ones(len(toks), dtype=bool) if not margins else np.min(np.array(margins, dtype=np.float64), axis=0) > gap
+
+
+def close_rows(got, cfg, W, toks, f32):
+    want = oracle(cfg, W, toks)
+    if f32:
+        return close(got, want, True)
+    keep = settled(cfg, W, toks)
+    assert keep.mean() > 0.5
+    return close(np.asarray(got)[keep], want[keep], False)
+
+
+def run_cut(model, toks, cuts, slot=0):
+    """feed toks in portions of the given sizes (the rest one by one); fp32 logits of every position"""
+    out, at = [], 0
+    sizes = list(cuts)
+    while at < len(toks):
+        n = sizes.pop(0) if sizes else 1
+        n = min(n, len(toks) - at)
+        lg, _ = model.forward_rows(toks[at:at + n], at, slot=slot, rows=list(range(n)))
+        out.append(lg)
+        at += n
+    return np.concatenate(out)
+
+
+def edited(cfg, fn, i=0):
+    """a copy of cfg whose layer i went through fn"""
+    c = json.loads(json.dumps(cfg))
+    fn(c["layers"][i])
+    return c
+
+
+# five different layers; the middle three run twice
+FULL = [layer(attn(), dense()),
+        layer(latent(), moe()),
+        layer(gru(), moe(experts=4, top=3, ff=10, groups=None, scale=0.8)),
+        layer(attn(heads=6, kv_heads=1, dim=16, block=33, rot_dims=4, base=50.0), None),
+        layer(latent(heads=2, dim=8, rot_dim=4, vdim=12, kv_rank=16, q_rank=24, scaling=False), dense(24, 0.7))]
+LOOP = (1, 4, 2)
+
+
+# ------------------------------------------------------------------------------------------------------------ each mechanism alone
+@pytest.mark.parametrize("f32", [True, False])
+@pytest.mark.parametrize("ly", [
+    layer(gru()),
+    layer(gru(70)),                                                              # channels that do not fill the last warp
+    layer(attn()),                                                               # grouped heads, part of each head rotated, blocks of 9
+    layer(attn(heads=3, kv_heads=3, dim=8, block=1, rot_dims=8)),                # no grouping, every entry rotated, a block of the token itself
+    layer(attn(heads=1, kv_heads=1, dim=70, block=0, rot_dims=0)),               # one wide head, every earlier position, no rotation
+    layer(attn(block=1000)),                                                     # a block longer than the model's context
+    layer(attn(rot_dims=12, base=200.0, scaling={"factor": 16.0, "original": 20, "fast": 2.0, "slow": 0.5})),  # stretched frequencies here too
+    layer(latent()),
+    layer(latent(heads=1, dim=6, rot_dim=2, vdim=70, kv_rank=9, q_rank=5, scaling=False)),   # one head, one rotated pair, wide values, odd ranks
+    layer(latent(heads=5, dim=16, rot_dim=8, vdim=16, kv_rank=24, q_rank=32)),               # row sizes that the tensor-core path takes in bf16
+    layer(latent(rot_dim=12, base=200.0, scaling={"factor": 16.0, "original": 20, "fast": 2.0, "slow": 0.5})),  # the ramp inside the table
+    layer(gru(), dense(56, 0.4)),                                                # both clamps bite
+    layer(gru(), moe()),                                                         # 2 of 6 experts from the best 2 of 3 groups
+    layer(gru(), moe(experts=5, top=2, groups=None)),                            # no groups
+    layer(gru(), moe(experts=8, top=4, groups=(2, 1))),                          # every expert of the one kept group
+    layer(gru(), moe(experts=4, top=2, groups=(4, 2))),                          # groups of one expert
+    layer(gru(), moe(experts=40, top=3, ff=8, groups=(5, 3))),                   # more experts than lanes
+], ids=["gru", "gru_70", "attn", "attn_block1", "attn_one_head_all", "attn_long_block", "attn_stretched", "latent", "latent_one_head", "latent_mma_sizes",
+        "latent_ramp", "dense_ff", "moe", "moe_no_groups", "moe_whole_group", "moe_groups_of_one", "moe_40"])
+def test_single_layer_prompt(ctx, ly, f32):
+    cfg = config([ly], width=32)
+    W = weights(cfg, seed=3)
+    toks = tokens(37, cfg["vocab"], 1)
+    m = build(ctx, cfg, W, f32)
+    got, _ = m.forward_rows(toks, 0, rows=list(range(len(toks))))
+    assert close_rows(got, cfg, W, toks, f32)
+    m.close()
+
+
+@pytest.mark.parametrize("loop", [None, (0, 3, 2), (1, 2, 3), (2, 3, 1), (0, 1, 4)])
+def test_repeated_layers(ctx, loop):
+    """a range of layers run several times on the same weights: every pass has its own cache and state, the embedding output returns before
+    the later passes, every pass (a single one too) gets its step vector; checked in a prompt, in portions and token by token"""
+    cfg = config([layer(gru(24), dense(16)), layer(attn(block=7), None), layer(latent(), moe())], width=32, loop=loop)
+    W = weights(cfg, seed=21)
+    toks = tokens(40, cfg["vocab"], 22)
+    want = oracle(cfg, W, toks)
+    if loop:
+        alt = dict(W)
+        alt["loop.step"] = bf16_grid(W["loop.step"] * 0.0)
+        assert rel(oracle(cfg, alt, toks), want) > 50 * TOL[True]
+    m = build(ctx, cfg, W, True)
+    assert rel(run_cut(m, toks, [40]), want) < TOL[True]
+    assert rel(run_cut(m, toks, [9, 2, 13]), want) < TOL[True]
+    m.close()
+
+
+def test_scales_and_norm_weights(ctx):
+    """norm weights far from 1 and a logit scale that is no power of two: a norm applied as 1 + w, or a head that is not scaled, shows"""
+    cfg = config([layer(gru(), dense(24))], width=32, logit_scale=0.37)
+    W = weights(cfg, seed=4)
+    for k in ("final.norm", "l0.norm1", "l0.norm2"):
+        W[k] = bf16_grid(W[k] * 3.0 - 0.5)
+    toks = tokens(20, cfg["vocab"], 2)
+    m = build(ctx, cfg, W, True)
+    assert rel(run_cut(m, toks, [9, 2]), oracle(cfg, W, toks)) < TOL[True]
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ whole stacks
+@pytest.mark.parametrize("f32", [True, False])
+def test_stack_prompt_and_decode(ctx, f32):
+    """a prompt in one step, then token by token: both equal the oracle; the first tokens of a sequence decoded one by one as well"""
+    cfg = config(FULL, loop=LOOP)
+    W = weights(cfg, seed=5)
+    toks = tokens(90, cfg["vocab"], 2)
+    m = build(ctx, cfg, W, f32)
+    assert close_rows(run_cut(m, toks, [64, 26]), cfg, W, toks, f32)          # two panels
+    assert close_rows(run_cut(m, toks, [50]), cfg, W, toks, f32)              # 50 at once, 40 decoded (graph replay from the second step on)
+    assert close_rows(run_cut(m, toks[:12], []), cfg, W, toks[:12], f32)       # from the very first token one by one
+    m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_wide_panels_and_tuned_matmul_widths(ctx, f32):
+    """width 128, extents that are multiples of 16, panels of up to 192 tokens: in bf16 the projections run on the tensor-core kernels and the
+    recurrence splits a panel into runs of tokens"""
+    cfg = config([layer(attn(heads=4, kv_heads=2, dim=32, block=70, rot_dims=16), dense(256)),
+                  layer(gru(128), moe(experts=8, top=2, ff=64, groups=(4, 2))),
+                  layer(latent(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=48), dense(128))], width=128, vocab=160, loop=(0, 2, 2))
+    W = weights(cfg, seed=14)
+    toks = tokens(230, cfg["vocab"], 15)
+    m = build(ctx, cfg, W, f32, panel=192, logit_rows=192)
+    assert close_rows(run_cut(m, toks, [192, 17, 2]), cfg, W, toks, f32)
+    m.close()
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_panel_attention_on_tensor_cores(ctx, hd):
+    """bf16, head size 64 / 128: panels of 16 tokens and more run the tile kernel (weights near 0 and 1, biases that matter, blocks of 75
+    positions whose edges fall inside 64-row tiles and inside panels, panels that start inside a tile, a ring of 75 + 63 rows that turns
+    twice); smaller portions and decoded tokens run the general kernel on the same ring rows"""
+    cfg = config([layer(attn(heads=4, kv_heads=2, dim=hd, block=75, rot_dims=hd // 2, base=1000.0), None)], width=64, vocab=80)
+    W = weights(cfg, seed=16, q_gain=4.0, pb=-1.5)
+    toks = tokens(300, cfg["vocab"], 17)
+    want = oracle(cfg, W, toks)
+    assert rel(oracle(edited(cfg, lambda l: l["mixer"]["mask"].update(size=74)), W, toks), want) > 2 * TOL[False]
+    assert rel(oracle(cfg, dict(W, **{"l0.mix.pb": W["l0.mix.pb"] * 0}), toks), want) > 2 * TOL[False]
+    m = build(ctx, cfg, W, False, max_seq=320)
+    assert close(run_cut(m, toks, [64, 17, 3, 64, 30, 2, 16, 40, 64]), want, False)
+    m.close()
+
+
+def test_portions_of_many_sizes(ctx):
+    cfg = config(FULL, loop=LOOP)
+    W = weights(cfg, seed=6)
+    toks = tokens(131, cfg["vocab"], 3)
+    want = oracle(cfg, W, toks)
+    m = build(ctx, cfg, W, True)
+    for cuts in ([2, 2, 3, 2, 64, 2, 31, 2, 17], [1, 2, 1, 63, 64, 1], [7] * 19, [64, 64, 2], [3, 1, 1, 2, 5, 64, 2, 2, 2, 40]):
+        assert rel(run_cut(m, toks, cuts), want) < TOL[True], cuts
+    m.close()
+
+
+def test_slots_reused_and_interleaved(ctx):
+    """two requests advance alternately in two slots; a released slot is taken by a new request and nothing of the old one shows"""
+    cfg = config(FULL, loop=LOOP)
+    W = weights(cfg, seed=7)
+    a, b, c = tokens(70, cfg["vocab"], 4), tokens(45, cfg["vocab"], 5), tokens(20, cfg["vocab"], 6)
+    wa, wb, wc = oracle(cfg, W, a), oracle(cfg, W, b), oracle(cfg, W, c)
+    m = build(ctx, cfg, W, True, slots=2)
+    sa, sb = m.acquire_slot(), m.acquire_slot()
+    assert {sa, sb} == {0, 1}
+    with pytest.raises(kf.KoifishError):
+        m.acquire_slot()
+    ga, gb, ia, ib = [], [], 0, 0
+    for na, nb in [(30, 2), (1, 20), (2, 1), (37, 22)]:
+        lg, _ = m.forward_rows(a[ia:ia + na], ia, slot=sa, rows=list(range(na)))
+        ga.append(lg), (ia := ia + na)
+        lg, _ = m.forward_rows(b[ib:ib + nb], ib, slot=sb, rows=list(range(nb)))
+        gb.append(lg), (ib := ib + nb)
+    assert rel(np.concatenate(ga), wa) < TOL[True] and rel(np.concatenate(gb), wb) < TOL[True]
+    m.release_slot(sa)
+    with pytest.raises(kf.KoifishError):
+        m.release_slot(sa)
+    sc = m.acquire_slot()
+    assert sc == sa  # the slot that held the 70-token request: states and rows of every pass still in place
+    assert rel(run_cut(m, c, [3, 2], slot=sc), wc) < TOL[True]
+    m.close()
+
+
+def test_batched_decode_of_unequal_requests(ctx):
+    """three sequences of different lengths take one token each in one step: every row equals the sequence run alone"""
+    cfg = config(FULL, loop=LOOP)
+    W = weights(cfg, seed=8)
+    seqs = [tokens(n, cfg["vocab"], 10 + n) for n in (41, 7, 18)]
+    m = build(ctx, cfg, W, True, slots=3)
+    for s, t in enumerate(seqs):
+        m.forward_rows(t[:-4], 0, slot=s)
+    for k in range(4, 0, -1):
+        lg, _ = m.forward_batch([t[len(t) - k] for t in seqs], [len(t) - k for t in seqs])
+        for s, t in enumerate(seqs):
+            assert rel(lg[s], oracle(cfg, W, t)[len(t) - k]) < TOL[True], (s, k)
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ shaped weights
+@pytest.mark.parametrize("f32", [True, False])
+def test_block_edges_and_head_bias(ctx, f32):
+    """sigmoid weights near 0 or 1 (query projections x 6) inside blocks of 23 positions with a bias per head: every key of the block counts
+    with its own weight, so a block that starts one position early or late, or a missing bias, moves the logits far beyond the gate -- the
+    oracle shows it first.  The framework then has to match in prompt panels (edges inside a panel and across panels), in small portions
+    and in decoding, over more than five turns of the ring (23 + 64 - 1 rows); the second layer has other blocks."""
+    cfg = config([layer(attn(heads=4, kv_heads=2, dim=16, block=23, rot_dims=12, base=100.0), None), layer(attn(block=37), dense(24))])
+    W = weights(cfg, seed=9, q_gain=6.0, pb=-2.0)
+    toks = tokens(520, cfg["vocab"], 7)
+    want = oracle(cfg, W, toks)
+    gate = 5 * TOL[f32]
+    assert rel(oracle(edited(cfg, lambda l: l["mixer"]["mask"].update(size=24)), W, toks), want) > gate
+    assert rel(oracle(edited(cfg, lambda l: l["mixer"]["mask"].update(size=22)), W, toks), want) > gate
+    assert rel(oracle(cfg, dict(W, **{"l0.mix.pb": W["l0.mix.pb"] * 0}), toks), want) > gate
+    assert rel(oracle(edited(cfg, lambda l: l["mixer"].pop("rot")), W, toks), want) > gate
+    m = build(ctx, cfg, W, f32, max_seq=640)
+    assert m.info.kv_bytes < 2 * 640 * (64 + 48) * (4 if f32 else 2) // 3  # rings of block + panel - 1 rows (64 and 48 entries), not max_seq rows
+    got = run_cut(m, toks, [64, 64, 23, 22, 24, 2, 2, 3, 64, 1, 64, 29])  # 362 in portions, then 158 decoded one by one
+    assert close(got, want, f32)
+    m.close()
+
+
+def test_long_decoding_through_the_ring(ctx):
+    """three tokens of prompt, then 300 decoded one by one with blocks of 7 (ring of 7 + 64 - 1 rows: four turns), all positions checked"""
+    cfg = config([layer(attn(block=7), dense(16)), layer(attn(block=64, rot_dims=12), None), layer(gru(24), None)], loop=(0, 2, 2))
+    W = weights(cfg, seed=10, q_gain=3.0)
+    toks = tokens(303, cfg["vocab"], 8)
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [3]), oracle(cfg, W, toks)) < TOL[True]
+    m.close()
+
+
+def test_nearly_closed_gates_keep_the_first_tokens(ctx):
+    """update gates around sigmoid(-6): the state after 300 tokens still holds the first thirty; cutting the sequence anywhere -- runs of a
+    panel, portions, single tokens -- leaves the logits alone"""
+    cfg = config([layer(gru(40), None), layer(gru(33), dense(24))], loop=(0, 1, 2))
+    W = weights(cfg, seed=10, z_bias=-6.0)
+    toks = tokens(300, cfg["vocab"], 8)
+    want = oracle(cfg, W, toks)
+    other = [(t + 1) % cfg["vocab"] for t in toks[:30]] + list(toks[30:])
+    assert rel(oracle(cfg, W, other)[-1], want[-1]) > 10 * TOL[True]  # the last logits do depend on tokens 270 and more positions back
+    m = build(ctx, cfg, W, True, max_seq=320)
+    assert rel(run_cut(m, toks, [64, 64, 1, 2, 1, 1, 3, 64, 2]), want) < TOL[True]  # ... then 98 decoded one by one
+    m.close()
+
+
+@pytest.mark.parametrize("f32", [True, False])
+def test_far_keys_in_a_peaked_softmax(ctx, f32):
+    """latent attention with the query up-projection x 6 over 640 positions: the softmax is peaked and the winning key lies anywhere, often
+    hundreds of positions back; prompts in panels, then decoding beyond position 512 where a token's keys are dealt to several CTAs"""
+    cfg = config([layer(latent(heads=4, dim=16, rot_dim=8, vdim=12, kv_rank=24, q_rank=20), None)])
+    W = weights(cfg, seed=18, q_gain=6.0)
+    toks = tokens(640, cfg["vocab"], 19)
+    want = oracle(cfg, W, toks)
+    short = oracle(cfg, W, toks[200:])  # the same tokens without their first 200: the late logits change, so far keys do carry weight
+    assert rel(short[-40:], want[-40:]) > 5 * TOL[f32]
+    m = build(ctx, cfg, W, f32, max_seq=700)
+    assert close(run_cut(m, toks, [64] * 9 + [3, 2]), want, f32)  # 581 in portions, then 59 decoded one by one
+    m.close()
+
+
+def test_selection_correction_and_groups_matter(ctx):
+    """a large selection correction and groups: the oracle without the correction, or with every group kept, gives other logits; the
+    framework follows the full rule, in a prompt and token by token"""
+    cfg = config([layer(gru(), moe(experts=12, top=3, ff=10, groups=(4, 2), scale=2.5))], width=32)
+    W = weights(cfg, seed=23, correction=1.0)
+    toks = tokens(60, cfg["vocab"], 24)
+    want = oracle(cfg, W, toks)
+    assert rel(oracle(cfg, dict(W, **{"l0.mlp.correction": W["l0.mlp.correction"] * 0}), toks), want) > 50 * TOL[True]
+    assert rel(oracle(edited(cfg, lambda l: l["mlp"]["router"]["groups"].update(keep=4)), W, toks), want) > 50 * TOL[True]
+    m = build(ctx, cfg, W, True)
+    assert rel(run_cut(m, toks, [33, 2]), want) < TOL[True]
+    m.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ kernels on their own
+def test_router_kernel_against_numpy(ctx):
+    """kf_moe_route_grouped alone, the one-block form (few tokens) and the many-token form, against a plain loop"""
+    rs = np.random.RandomState(3)
+    for M, E, top, groups, keep in ((5, 12, 3, 4, 2), (300, 64, 6, 8, 3), (70, 96, 4, 3, 1), (9, 7, 2, 1, 1)):
+        lg = rs.randn(M, E).astype(np.float32) * 2
+        corr = bf16_grid(torch.from_numpy(rs.randn(E).astype(np.float32)))
+        n = M * top
+        idx, wgt = ctx.zeros(n * 4), ctx.zeros(n * 4)
+        offs, es, sr, sg, work = ctx.zeros((E + 1) * 4), ctx.zeros(n * 4), ctx.zeros(n * 4), ctx.zeros(n * 4), ctx.zeros((2 * n + E) * 4)
+        lgd, cd = ctx.array(lg), ctx.array(bits(corr))
+        ctx.check(ctx.lib.kf_moe_route_grouped(ctx.h, idx.ptr, wgt.ptr, offs.ptr, es.ptr, sr.ptr, sg.ptr, work.ptr, lgd.ptr, E, cd.ptr, M, E, top, groups, keep, 1.5),
+                  "kf_moe_route_grouped")
+        gi, gw = idx.numpy(np.int32, (M, top)), wgt.numpy(np.float32, (M, top))
+        s = 1.0 / (1.0 + np.exp(-lg.astype(np.float64)))
+        ch = s + corr.numpy().astype(np.float64)
+        per = E // groups
+        for t in range(M):
+            score = [np.sort(ch[t, g * per:(g + 1) * per])[-2:].sum() for g in range(groups)]
+            kept = sorted(range(groups), key=lambda g: (-score[g], g))[:keep]
+            cand = [e for e in range(E) if e // per in kept]
+            want = sorted(cand, key=lambda e: (-ch[t, e], e))[:top]
+            assert list(gi[t]) == want, (M, E, t)
+            assert np.allclose(gw[t], 1.5 * s[t, want], rtol=1e-5)
+        off = offs.numpy(np.int32, (E + 1,))
+        assert off[0] == 0 and off[E] == n and np.array_equal(np.diff(off), np.bincount(gi.reshape(-1), minlength=E))
+        slot_group, slot_row, entry = sg.numpy(np.int32, (n,)), sr.numpy(np.int32, (n,)), es.numpy(np.int32, (n,))
+        assert np.array_equal(slot_group[entry], gi.reshape(-1)) and np.array_equal(slot_row[entry], np.arange(n) // top)
+
+
+def test_sigmoid_attention_kernel_options(ctx):
+    """kf_qk_prepare_ex + kf_attn_sigmoid alone with what the stack does not use: neighbouring rotation pairs, a window inside the block, an
+    output factor, no head bias, a float ring, a sequence joined late"""
+    rs = np.random.RandomState(5)
+    M, H, G, dk, rot, ring = 11, 4, 2, 12, 8, 16
+    nq, nk = H * dk, G * dk
+    x = rs.randn(M, nq + nk).astype(np.float32)
+    qb, kb = bf16_grid(torch.from_numpy(rs.randn(nq).astype(np.float32))), bf16_grid(torch.from_numpy(rs.randn(nk).astype(np.float32)))
+    freq = (50.0 ** (-2.0 * np.arange(rot // 2) / rot)).astype(np.float64)
+    pos = np.arange(M, dtype=np.int32) + 3
+    xd, fd, pd, sd = ctx.array(x), ctx.array(freq), ctx.array(pos), ctx.array(np.zeros(M, dtype=np.int32))
+    cache = ctx.zeros(ring * 2 * nk * 4)
+    qbd, kbd = ctx.array(bits(qb)), ctx.array(bits(kb))
+    ctx.check(ctx.lib.kf_qk_prepare_ex(ctx.h, xd.ptr, nq + nk, nq, nk, nk, dk, qbd.ptr, kbd.ptr, 1, None, None, 1e-5, rot, fd.ptr, 1.5, 0, cache.ptr, 1,
+                                       ring * 2 * nk, ring, None, pd.ptr, sd.ptr, M), "kf_qk_prepare_ex")
+
+    def turn(v, p):  # v [heads, dk], pairs (2i, 2i + 1)
+        out = v.copy()
+        a = p * freq
+        ev, od = v[:, 0:rot:2], v[:, 1:rot:2]
+        out[:, 0:rot:2] = 1.5 * (ev * np.cos(a) - od * np.sin(a))
+        out[:, 1:rot:2] = 1.5 * (od * np.cos(a) + ev * np.sin(a))
+        return out
+
+    qf = x[:, :nq].astype(np.float64) + qb.numpy()
+    kf_ = x[:, nq:].astype(np.float64) + kb.numpy()
+    q = np.stack([turn(qf[t].reshape(H, dk), pos[t]) for t in range(M)])
+    k = np.stack([turn(kf_[t].reshape(G, dk), pos[t]) for t in range(M)])
+    rows = cache.numpy(np.float32, (ring, 2 * nk))
+    for t in range(M):
+        assert np.abs(rows[pos[t] % ring, :nk].reshape(G, dk) - k[t]).max() < 2e-6 * np.abs(k).max()
+        assert np.abs(rows[pos[t] % ring, nk:] - kf_[t]).max() < 1e-6  # the values: the keys before the rotation, with their bias
+    got_q = xd.numpy(np.float32, (M, nq + nk))[:, :nq]
+    out = ctx.empty(M * nq * 4)
+    # blocks of 8 positions, a window of 5, no bias, factor 0.5; positions 3 .. 13: block edges at 8
+    qd = ctx.array(np.ascontiguousarray(got_q))
+    ctx.check(ctx.lib.kf_attn_sigmoid(ctx.h, out.ptr, 1, nq, qd.ptr, nq, cache.ptr, 1, ring * 2 * nk, ring, None, pd.ptr, sd.ptr, M, H, G, dk, dk, 0.3, 8, 5, 16, 0.5),
+              "kf_attn_sigmoid")
+    got = out.numpy(np.float32, (M, nq)).reshape(M, H, dk)
+    for t in range(M):
+        lo = max((pos[t] // 8) * 8, pos[t] - 4, 3)
+        js = [j - 3 for j in range(lo, pos[t] + 1)]
+        for h in range(H):
+            g = h // (H // G)
+            w = 1.0 / (1.0 + np.exp(-(k[js, g] @ q[t, h]) * 0.3))
+            assert np.abs(got[t, h] - 0.5 * (w[:, None] * kf_[js].reshape(len(js), G, dk)[:, g]).sum(0)).max() < 1e-5, (t, h)
+
+
+# ------------------------------------------------------------------------------------------------------------ entry points
+def test_greedy_generation(ctx):
+    cfg = config(FULL, loop=LOOP)
+    W = weights(cfg, seed=11)
+    prompt = tokens(70, cfg["vocab"], 9)  # longer than a panel
+    seq = list(prompt)
+    for _ in range(12):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    m = build(ctx, cfg, W, True)
+    out, why = m.generate(prompt, 12)
+    assert out == seq[len(prompt):] and why == 2
+    m.close()
+
+
+def test_command_line_on_a_checkpoint_folder(ctx, tmp_path):
+    """config.json + model.safetensors on disk -> `generate` and `trace` of the command line, both number formats; optional keys left out of
+    the file (kv_heads, vdim, scale, q_rank, the groups, the logit scale) take their defaults or come from the tensors' shapes"""
+    cfg = config([layer(attn(heads=3, kv_heads=3), dense()), layer(latent(), moe(groups=(1, 1), scale=1.0)), layer(gru(), None)], loop=(0, 2, 2), logit_scale=1.0)
+    W = weights(cfg, seed=12)
+    disk = json.loads(json.dumps(cfg))
+    disk.pop("logit_scale")
+    a0, a1 = disk["layers"][0]["mixer"], disk["layers"][1]["mixer"]
+    a0.pop("kv_heads"), a0.pop("vdim"), a0.pop("scale"), a1.pop("scale"), a1.pop("q_rank")
+    r = disk["layers"][1]["mlp"]["router"]
+    r.pop("groups"), r.pop("scale")
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(disk))
+    write_safetensors(str(d / "model.safetensors"), [(k, "BF16", bits(v).reshape(v.shape)) for k, v in W.items()])
+    a, b = tokens(75, cfg["vocab"], 13), tokens(9, cfg["vocab"], 14)
+    wa, wb = oracle(cfg, W, a), oracle(cfg, W, b)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:70], "want": [0, 5, 69]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[70:72], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[72:], "want": [2, 1]}], "end": ["x"]},
+             {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [8]}], "end": ["y"]}]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / ("out_" + dtype)
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(d), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+        assert not (out / "1.f32").exists()
+        f = lambda n: np.fromfile(str(out / ("%d.f32" % n)), dtype="<f4").reshape(-1, cfg["vocab"])
+        got, want = np.concatenate([f(0), f(2), f(3)]), np.concatenate([wa[[0, 5, 69]], wa[[74, 73]], wb[[8]]])
+        keep = np.ones(6, dtype=bool) if dtype == "float32" else np.concatenate([settled(cfg, W, a)[[0, 5, 69, 74, 73]], settled(cfg, W, b)[[8]]])
+        assert keep.sum() >= 4 and close(got[keep], want[keep], dtype == "float32")
+    r = subprocess.run([sys.executable, "-m", "koifish_b200.cli", "generate", "--model", str(d), "--ids", ",".join(map(str, b)), "--max-new-tokens", "5"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    seq = list(b)
+    for _ in range(5):
+        seq.append(int(np.argmax(oracle(cfg, W, seq)[-1])))
+    got = json.loads(r.stdout.strip().splitlines()[-1])["tokens"]
+    assert len(got) == 5 and got[0] == seq[len(b)]  # bf16 serving: the first token is far from a tie; later ones may legitimately differ
