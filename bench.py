@@ -2,7 +2,7 @@
 """bench.py -- decode throughput of the quantized-inference hot path (BASELINE.json metric: decode tokens/s, Qwen3 4-bit).
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload qwen3-32b-q4] [--ctx 512]
-    python bench.py --compare-arch sipazen|kivorax|sedotar [--arch-sizes s,m] [--prompt 2048] [--panel 512]     (another architecture beside Qwen3; own output)
+    python bench.py --compare-arch sipazen|kivorax|sedotar|fazolorn [--arch-sizes s,m] [--prompt 2048] [--panel 512]     (another architecture beside Qwen3; own output)
 
 A "step" is one decode token (one pass of the hot path: 64 x [RMSNorm, fused-dequant QKV GEMV, QK-norm+RoPE+KV append, split-K
 GQA attention, O GEMV+residual, RMSNorm, gate/up GEMV+SwiGLU, down GEMV+residual] + final norm + lm_head GEMV + argmax).
@@ -206,7 +206,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (INVALID as a bench number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--compare-arch", default="", choices=["", "sipazen", "kivorax", "sedotar"],
+    ap.add_argument("--compare-arch", default="", choices=["", "sipazen", "kivorax", "sedotar", "fazolorn"],
                     help="instead of the default workload: prefill / decode throughput of this architecture beside Qwen3 at equal size (koifish_b200/bench_arch.py)")
     ap.add_argument("--arch-sizes", default="s,m", help="--compare-arch: size presets, comma separated (s, m, l)")
     ap.add_argument("--prompt", type=int, default=2048, help="--compare-arch: prompt length = decode context")

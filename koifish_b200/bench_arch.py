@@ -1,8 +1,9 @@
-"""Prefill and decode throughput of a hybrid stack (bench.py --compare-arch sipazen | kivorax | sedotar) beside the closest existing models
-at equal width, depth and active feed-forward width: Sipazen beside Qwen3; Kivorax beside Sipazen (the other recurrence + attention +
+"""Prefill and decode throughput of a hybrid stack (bench.py --compare-arch sipazen | kivorax | sedotar | fazolorn) beside the closest existing
+models at equal width, depth and active feed-forward width: Sipazen beside Qwen3; Kivorax beside Sipazen (the other recurrence + attention +
 experts stack of this runtime) and Qwen3; Sedotar (sliding-window attention beside a delta rule, dense feed-forward) beside Kivorax with
-dense feed-forwards (delta-rule layers and attention layers alternating) and Qwen3.  All bf16 with random weights.  One JSON line per
-(model, size).
+dense feed-forwards (delta-rule layers and attention layers alternating) and Qwen3; Fazolorn (minGRU, sigmoid block attention and latent
+attention layers with routed experts) beside Sipazen (state-space and latent attention layers with routed experts) and Qwen3.  All bf16
+with random weights.  One JSON line per (model, size).
 
     prefill: a prompt of --prompt tokens through the model's own step function in panels, timed with CUDA events after 3 warm-up prompts
     decode : the device-resident greedy loop (one CUDA-graph replay per token) at context --prompt, after W warm-up tokens
@@ -78,6 +79,28 @@ def sedotar_config(p):
     return {"architecture": "Sedotar", "vocab": p["vocab"], "width": w, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": [ly] * len(p["pattern"])}
 
 
+def fazolorn_config(p):
+    """as many layers as the preset's pattern, in the order sigmoid block attention (head size 128, 4 query heads per kv head, half of each
+    head rotated, blocks of 1024 positions), minGRU (2 x width channels), latent attention (the preset's sizes, queries through a latent of
+    1.5 x kv_rank, stretched frequencies); the first feed-forward dense and clamped, the others routed experts (the preset's count and top,
+    4 groups of which 2 are kept) whose width makes the active width equal to the preset's experts + shared expert"""
+    w, a, m = p["width"], p["att"], p["moe"]
+    heads = w // 128
+    ff = (m["ff"] + m["shared"] // m["top"] + 127) // 128 * 128
+    mixers = [("attention", dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=1024), rot=dict(base=1e6, dims=64))),
+              ("mingru", dict(width=2 * w)),
+              ("latent_attention", dict(a, q_rank=a["kv_rank"] * 3 // 2, scale=(a["dim"] + a["rot_dim"]) ** -0.5,
+                                        rot=dict(base=1e6, dims=a["rot_dim"], scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0))))]
+    layers = []
+    for i in range(len(p["pattern"])):
+        typ, mixer = mixers[i % 3]
+        mlp = {"kind": "dense", "ff": m["top"] * ff, "limit": 7.0} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": m["experts"], "top": m["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+        layers.append({"type": typ, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Fazolorn", "vocab": p["vocab"], "width": w, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
+            "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers}
+
+
 def kivorax_dense_config(p):
     """Kivorax at the size of sedotar_config: delta-rule layers and attention (+ LRU) layers alternating, a dense feed-forward of the same
     width in every layer, no side input"""
@@ -131,6 +154,8 @@ def run(args, ctx, stream):
             kcfg = kivorax_config(p)
             cfgs["kivorax"] = {"hf_config": kcfg, "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
                                "init": {"sigma": 0.02, "norm_sigma": 0.02}}
+        if args.compare_arch == "fazolorn":
+            cfgs["fazolorn"] = {"hf_config": fazolorn_config(p), "gpt": dict(gpt), "init": {"sigma": 0.02, "norm_sigma": 0.02}}
         if args.compare_arch != "sedotar":
             cfgs["sipazen"] = {"hf_config": sipazen_config(p), "gpt": {"max_seq_len": P + args.steps + args.warmup + 64, "max_batch": 1, "max_prefill": panel},
                                "init": {"sigma": 0.02, "norm_sigma": 0.02}}
