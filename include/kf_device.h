@@ -383,7 +383,7 @@ int kf_glu_clamped(kf_ctx* ctx, void* out_dev, int out_f32, int ldo, const float
                    float limit, float alpha, float shift);
 int kf_scale_f32(kf_ctx* ctx, float* x_dev, size_t n, float s); /* x *= s */
 /* kf_moe_route's tables from sigmoid scores: the choice runs over sigmoid(logit) + choice_bias inside the `keep` best of `groups` equal groups
- * of neighbouring experts (a group ranks by the sum of its two largest choice values); weights = scale * sigmoid(logit), not renormalised */
+ * of adjacent experts (a group ranks by the sum of its top-2 choice values); weights = scale * sigmoid(logit), not renormalised */
 int kf_moe_route_grouped(kf_ctx* ctx, int32_t* idx_dev, float* wgt_dev, int32_t* offsets_dev, int32_t* entry_slot_dev, int32_t* slot_row_dev,
                          int32_t* slot_group_dev, int32_t* work_dev, const float* logits_dev, int ldl, const void* choice_bias_bf16_dev, int M, int E, int top,
                          int groups, int keep, float scale);

@@ -95,7 +95,7 @@ def fazolorn_config(p):
     for i in range(len(p["pattern"])):
         typ, mixer = mixers[i % 3]
         mlp = {"kind": "dense", "ff": m["top"] * ff, "limit": 7.0} if i == 0 else \
-            {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": m["experts"], "top": m["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+            {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": m["experts"], "top": m["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
         layers.append({"type": typ, "mixer": mixer, "mlp": mlp})
     return {"architecture": "Fazolorn", "vocab": p["vocab"], "width": w, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
             "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers}

@@ -562,7 +562,7 @@ struct PfBias {
     int out_ld;       // MODE 2, 3: elements between the output rows of consecutive tokens
     float out_scale;  // MODE 2, 3: factor on the result before it is rounded
     // MODE 3 (sigmoid weights inside blocks of positions): a query at p sees the positions t <= p of its own block of `block` positions,
-    // counted from position 0 (0x7fffffff: one block); the weight of a key is sigmoid(scale q.k + hbias[h]) (bf16 [n_head] or NULL); the
+    // aligned to position 0 (0x7fffffff: one block); the weight of a key is sigmoid(scale q.k + hbias[h]) (bf16 [n_head] or NULL); the
     // weights are not normalised over the keys
     int block;
     const uint16_t* hbias;

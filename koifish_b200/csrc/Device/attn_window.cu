@@ -33,7 +33,7 @@ struct PrepArgs {
     int ldx, nq, nk, nv, hd;
     const uint16_t *qw, *kw;  // bf16 [nq], [nk] or NULL (that row is not normed)
     const uint16_t *qb_add, *kb_add;  // bf16 [nq], [nk] or NULL: biases added to q and k before anything else
-    int v_from_k;             // 1: the cached values are the keys as they are before the rotation (x holds no v; nv == nk)
+    int v_from_k;             // 1: v is a copy of k taken ahead of the rotation (x holds no v; nv == nk)
     float eps, amp;
     int rot_dims, layout;     // layout 0: pairs (2i, 2i+1); 1: pairs (i, i + rot_dims / 2)
     const double* inv_freq;   // [rot_dims / 2]
@@ -257,7 +257,7 @@ __global__ void kf_attn_window_merge_kernel(WinArgs a) {
     }
 }
 // ---- sigmoid-weighted attention: o_i = sum_j sigmoid(scale q_i . k_j + b_h) v_j over the visible keys, NOT normalised over the keys.
-// Visible: j <= i, j in the block of `block` positions that holds i (blocks counted from position 0; block 0: none), and inside the window
+// Visible: j <= i, j in the block of `block` positions that holds i (blocks aligned to position 0; block 0: none), and inside the window
 // when one is given.  Same work split as kf_attn_window_kernel (CTA per (token, head, key split), a lane per key for the scores, lanes over
 // the value entries for the sum); the splits' partial sums are added in split order.
 __device__ __forceinline__ float sig_f(float z) { return 1.f / (1.f + expf(-z)); }
@@ -427,7 +427,7 @@ extern "C" int kf_attn_window(kf_ctx* ctx, void* out, int out_f32, int ldo, cons
 }
 
 // out [M][ldo] (heads x dv, activation type) = sum over the visible keys j of sigmoid(scale q . k_j + head_bias[h]) v_j -- no softmax, the
-// weights are not normalised.  Visible: positions <= pos[m] inside the block of `block` consecutive positions (counted from position 0) that
+// weights are not normalised.  Visible: positions <= pos[m] inside the block of `block` consecutive positions (aligned to position 0) that
 // holds pos[m] (block <= 0: every earlier position), and inside the last `window` positions when window > 0.  Cache rows as in
 // kf_attn_window ([k | v] per position in a ring); the ring must cover a block (and every position when there are no blocks and no window).
 extern "C" int kf_attn_sigmoid(kf_ctx* ctx, void* out, int out_f32, int ldo, const float* q, int ldq, const void* cache, int cache_f32, size_t slot_stride,

@@ -299,12 +299,15 @@ __global__ void __launch_bounds__(32 * LRU_W) kf_rglru_scan_kernel(TO* __restric
     }
     if (w == W - 1) *st = s;  // the last run ends at token T - 1 (runs may be empty only at the end when T < W, which the launch rules out)
 }
-// minGRU: a channel-wise gated recurrence whose gates read only the current token,
+// minGRU: per channel a gated recurrence; update gate and candidate are functions of the same position's input alone,
 //     z = sigmoid(zl + zb),   u = xl + xb,   c = u + 1/2 (u >= 0) | sigmoid(u) (u < 0),   s <- (1 - z) s + z c,   out = s * silu(gl)
-// with 1 - z formed as sigmoid(-(zl + zb)).  Same launch shape as kf_rglru_scan_kernel: a CTA owns 32 channels, its warps runs of consecutive
-// tokens; a first pass reduces every run to one affine map, a second replays it from the run's incoming state.  The gates are recomputed
-// in the second pass (no work buffer).
-template <typename TO>
+// with 1 - z formed as sigmoid(-(zl + zb)), not by subtraction.  Same launch shape as kf_rglru_scan_kernel: a CTA owns 32 channels, its warps runs of consecutive
+// tokens; a first pass reduces every run to one affine map, a second replays it from the run's incoming state.  STASH: a run has at most
+// MINGRU_RUN tokens and the first pass leaves (1 - z, z c) of each in registers -- all its loads are independent and in flight together --
+// so the second pass reads only gl; otherwise the gates are recomputed in the second pass.  Both forms do the same fp32 operations in the
+// same order.
+constexpr int MINGRU_RUN = 32;
+template <typename TO, bool STASH>
 __global__ void __launch_bounds__(32 * LRU_W) kf_mingru_kernel(TO* __restrict__ out, int ldo, const float* __restrict__ zl, int ldz, const uint16_t* __restrict__ zb,
                                                                const float* __restrict__ xl, int ldx, const uint16_t* __restrict__ xb,
                                                                const float* __restrict__ gl, int ldg, float* __restrict__ state, size_t state_stride,
@@ -317,35 +320,83 @@ __global__ void __launch_bounds__(32 * LRU_W) kf_mingru_kernel(TO* __restrict__ 
     float* st = state + (size_t)slot[m0] * state_stride + (live ? ch : 0);
     float s = (pos[m0] == 0 || !live) ? 0.f : *st;
     const float bz = (live && zb) ? bf16_bits_to_f32(zb[ch]) : 0.f, bx = (live && xb) ? bf16_bits_to_f32(xb[ch]) : 0.f;
-    auto gates = [&](size_t m, float& keep, float& add) {
-        const float zv = zl[m * ldz + ch] + bz, u = xl[m * ldx + ch] + bx;
-        keep = sigmoid_f(-zv);
-        add  = sigmoid_f(zv) * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
+    // (1 - z, z c) from the two logits; z and 1 - z share one exponential: e = exp(-|zv|), the larger of the two is 1 / (1 + e), the smaller
+    // e / (1 + e), either accurate to fp32 rounding however large |zv| is
+    auto mix = [&](float zv, float u, float& keep, float& add) {
+        const float e = expf(-fabsf(zv)), big = 1.f / (1.f + e), small = e * big;
+        keep = zv >= 0.f ? small : big;
+        add  = (zv >= 0.f ? big : small) * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
+    };
+    auto gates = [&](size_t m, float& keep, float& add) { mix(zl[m * ldz + ch] + bz, xl[m * ldx + ch] + bx, keep, add); };
+    auto emit = [&](size_t m, float sv) {
+        const float g = gl[m * ldg + ch];
+        const float o = sv * g * sigmoid_f(g);
+        if (sizeof(TO) == 2) ((uint16_t*)out)[m * ldo + ch] = f32_to_bf16_bits(o);
+        else ((float*)out)[m * ldo + ch] = o;
     };
     float P = 1.f, B = 0.f;
-    if (W > 1 && live) {
+    if (STASH) {
+        // loads first, all of them independent and in flight together, the arithmetic after them; a token past the run's end is not read
+        // and contributes the identity map
+        float kp[MINGRU_RUN], ad[MINGRU_RUN];
+        const int nrun = live ? t_hi - t_lo : 0;
+        const float* zp = zl + (size_t)(m0 + t_lo) * ldz + ch;
+        const float* xp = xl + (size_t)(m0 + t_lo) * ldx + ch;
+#pragma unroll
+        for (int i = 0; i < MINGRU_RUN; i++) {
+            kp[i] = i < nrun ? zp[(size_t)i * ldz] : 0.f;
+            ad[i] = i < nrun ? xp[(size_t)i * ldx] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < MINGRU_RUN; i++) {
+            float keep, add;
+            mix(kp[i] + bz, ad[i] + bx, keep, add);
+            kp[i] = i < nrun ? keep : 1.f;
+            ad[i] = i < nrun ? add : 0.f;
+            B = fmaf(kp[i], B, ad[i]), P *= kp[i];
+        }
+        sP[w][lane] = P, sB[w][lane] = B;
+        __syncthreads();
+        for (int q = 0; q < w; q++) s = fmaf(sP[q][lane], s, sB[q][lane]);
+        if (!live) return;
+        const float* gp = gl + (size_t)(m0 + t_lo) * ldg + ch;
+        TO* op = out + (size_t)(m0 + t_lo) * ldo + ch;
+#pragma unroll
+        for (int i0 = 0; i0 < MINGRU_RUN; i0 += 8) {
+            float g[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) g[j] = i0 + j < nrun ? gp[(size_t)(i0 + j) * ldg] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (i0 + j < nrun) {
+                    s = fmaf(kp[i0 + j], s, ad[i0 + j]);
+                    const float o = s * g[j] * sigmoid_f(g[j]);
+                    if (sizeof(TO) == 2) op[(size_t)(i0 + j) * ldo] = (TO)f32_to_bf16_bits(o);
+                    else op[(size_t)(i0 + j) * ldo] = (TO)o;
+                }
+            }
+        }
+    } else {
+        if (W > 1 && live) {
+#pragma unroll 4
+            for (int t = t_lo; t < t_hi; t++) {
+                float keep, add;
+                gates((size_t)(m0 + t), keep, add);
+                B = fmaf(keep, B, add);
+                P *= keep;
+            }
+        }
+        sP[w][lane] = P, sB[w][lane] = B;
+        __syncthreads();
+        for (int q = 0; q < w; q++) s = fmaf(sP[q][lane], s, sB[q][lane]);
+        if (!live) return;
 #pragma unroll 4
         for (int t = t_lo; t < t_hi; t++) {
             float keep, add;
             gates((size_t)(m0 + t), keep, add);
-            B = fmaf(keep, B, add);
-            P *= keep;
+            s = fmaf(keep, s, add);
+            emit((size_t)(m0 + t), s);
         }
-    }
-    sP[w][lane] = P, sB[w][lane] = B;
-    __syncthreads();
-    for (int q = 0; q < w; q++) s = fmaf(sP[q][lane], s, sB[q][lane]);
-    if (!live) return;
-#pragma unroll 4
-    for (int t = t_lo; t < t_hi; t++) {
-        const size_t m = (size_t)(m0 + t);
-        float keep, add;
-        gates(m, keep, add);
-        s = fmaf(keep, s, add);
-        const float g = gl[m * ldg + ch];
-        const float o = s * g * sigmoid_f(g);
-        if (sizeof(TO) == 2) ((uint16_t*)out)[m * ldo + ch] = f32_to_bf16_bits(o);
-        else ((float*)out)[m * ldo + ch] = o;
     }
     if (t_hi == T && t_lo < T) *st = s;  // the run that ends at the last token leaves the state
 }
@@ -360,12 +411,18 @@ extern "C" int kf_mingru(kf_ctx* ctx, void* out, int out_f32, int ldo, const flo
     KF_REQUIRE(ctx, nseq >= 1 && T >= 1 && width >= 1 && state_stride >= (size_t)width, "shape");
     dim3 grid((width + 31) / 32, nseq);
     const int warps = std::max(1, std::min(LRU_W, T / 8)), threads = 32 * warps;  // runs of at least 8 tokens; one warp when decoding
-    if (out_f32)
-        kf_mingru_kernel<float><<<grid, threads, 0, ctx->stream>>>((float*)out, ldo, z_logit, ldz, (const uint16_t*)z_bias_bf16, x_logit, ldx,
-                                                               (const uint16_t*)x_bias_bf16, g_logit, ldg, state, state_stride, pos_dev, slot_dev, T, width);
-    else
-        kf_mingru_kernel<uint16_t><<<grid, threads, 0, ctx->stream>>>((uint16_t*)out, ldo, z_logit, ldz, (const uint16_t*)z_bias_bf16, x_logit, ldx,
-                                                                  (const uint16_t*)x_bias_bf16, g_logit, ldg, state, state_stride, pos_dev, slot_dev, T, width);
+    const bool stash = warps > 1 && (T + warps - 1) / warps <= MINGRU_RUN;  // one warp (decoding): the short form, less code to fetch
+#define KF_MINGRU_LAUNCH(TO, ST)                                                                                                              \
+    kf_mingru_kernel<TO, ST><<<grid, threads, 0, ctx->stream>>>((TO*)out, ldo, z_logit, ldz, (const uint16_t*)z_bias_bf16, x_logit, ldx,      \
+                                                                (const uint16_t*)x_bias_bf16, g_logit, ldg, state, state_stride, pos_dev, slot_dev, T, width)
+    if (out_f32) {
+        if (stash) KF_MINGRU_LAUNCH(float, true);
+        else KF_MINGRU_LAUNCH(float, false);
+    } else {
+        if (stash) KF_MINGRU_LAUNCH(uint16_t, true);
+        else KF_MINGRU_LAUNCH(uint16_t, false);
+    }
+#undef KF_MINGRU_LAUNCH
     KF_LAUNCH_CHECK(ctx);
     return KF_OK;
 }

@@ -196,8 +196,8 @@ __global__ void kf_f32_to_bf16_kernel(uint16_t* __restrict__ out, const float* _
 
 // ---- mixture of experts ---------------------------------------------------------------------------------------------------
 // How a token's experts are chosen and weighted.  kind 0: arg-max over logits (+ bias), weights from a softmax (the kernels' `full` flag).
-// kind 1: scores s = sigmoid(logit); the choice runs over s + bias; the experts form `groups` equal groups of neighbours, a group is ranked
-// by the sum of its two largest choice values and only the `keep` best groups can be chosen from; weights = scale * s of the chosen, not
+// kind 1: scores s = sigmoid(logit); the choice runs over s + bias; the experts form `groups` equal contiguous groups, a group is ranked
+// by the sum of its top-2 choice values and only the `keep` best groups can be chosen from; weights = scale * s of the chosen, not
 // renormalised.
 struct RouteMode {
     int kind, groups, keep;
@@ -207,7 +207,7 @@ struct RouteMode {
 __device__ __forceinline__ void route_grouped_warp(int* taken, int32_t* idx, float* __restrict__ wgt, const float* __restrict__ lg,
                                                    const uint16_t* __restrict__ bias, int E, int top, const RouteMode md, int lane) {
     const int per = E / md.groups;
-    // lane g keeps the rank value of group g (groups <= 32): the two largest choice values of the group, found by all lanes together
+    // lane g keeps the rank value of group g (groups <= 32): the top-2 choice values of the group, found by all lanes together
     float gscore = -INFINITY;
     for (int g = 0; g < md.groups; g++) {
         float a = -INFINITY, b = -INFINITY;  // largest, second largest of this lane's share
@@ -605,7 +605,7 @@ extern "C" int kf_moe_route_ex(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* o
     return moe_route_impl(ctx, idx, wgt, offsets, entry_slot, slot_row, slot_group, work, logits, ldl, bias_bf16, M, E, top, full_softmax, md);
 }
 // The same tables from sigmoid scores: the choice runs over sigmoid(logit) + choice_bias (bf16 [E] or NULL) inside the `keep` best of
-// `groups` equal groups of neighbouring experts (a group ranks by the sum of its two largest choice values; groups <= 32, groups 1: no
+// `groups` equal contiguous groups of experts (a group ranks by the sum of its top-2 choice values; groups <= 32, groups 1: no
 // grouping); weights = scale * sigmoid(logit) of the chosen experts, not renormalised.  top <= keep * (E / groups).
 extern "C" int kf_moe_route_grouped(kf_ctx* ctx, int32_t* idx, float* wgt, int32_t* offsets, int32_t* entry_slot, int32_t* slot_row, int32_t* slot_group,
                                     int32_t* work, const float* logits, int ldl, const void* choice_bias_bf16, int M, int E, int top, int groups, int keep,

@@ -84,7 +84,7 @@ static void ParseFazolorn(const JSON& h, MODEL_CARD& c) {
             if (const JSON* k = present(x, "mask")) m.block = need_int(*k, "size", wm + ".mask");
             if (m.heads < 1 || m.kv_heads < 1 || m.heads % m.kv_heads || m.dim < 1 || m.dim > 512 || m.block < 0)
                 throw std::runtime_error("config: " + wm + ": kv_heads must divide heads, 1 <= dim <= 512, mask.size >= 0");
-            if (m.vdim != m.dim) throw std::runtime_error("config: " + wm + ": the values are the keys, so vdim must equal dim");
+            if (m.vdim != m.dim) throw std::runtime_error("config: " + wm + ": v is the un-rotated k, so vdim must equal dim");
             parse_rot(x, m, m.dim, m.dim, wm);
         } else if (m.type == "latent_attention") {
             m.heads = need_int(x, "heads", wm), m.dim = need_int(x, "dim", wm), m.rot_dim = need_int(x, "rot_dim", wm);
@@ -399,7 +399,7 @@ int BlockAttention::cuInfer(int M, float* u, int ldu, int off, int cache) {
     SeqStateCache::Layer& sl = f.states.layers[cache];
     // a block longer than the ring means the ring was cut to max_seq rows: every position lies in block 0 and none is ever masked
     const int blk = m.block <= sl.ring ? m.block : 0;
-    // biases, rotation of q (in place) and k; the row [rotated k | k as projected] joins the ring: the values are the unrotated keys
+    // biases, rotation of q (in place) and k; the row [rotated k | un-rotated k] joins the ring: the second half serves as v
     // panels of one sequence with head sizes the tensor-core kernel takes go there; everything else (decode, other sizes, 32-bit) to the general kernel
     const bool tile = !ak && f.panel_consecutive && f.seq_mode == 0 && M >= 16 && (m.dim == 64 || m.dim == 128);
     KF_TRY(kf_qk_prepare_ex(f.ctx, u + off, ldu, nq, nk, nk, m.dim, q_b->data, k_b->data, 1, nullptr, nullptr, c.norm_rms_eps, m.rot_dims, inv_freq, amp, 1, sl.rows,

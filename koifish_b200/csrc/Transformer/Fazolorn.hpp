@@ -4,9 +4,9 @@
 // own -- and, before pass t, x += [t > 0] (the embedding output) + step[t].  Mixers:
 //   MinGRU              z = sigmoid(W_z h + b_z), u = W_x h + b_x, c = u + 1/2 (u >= 0) | sigmoid(u);  s <- (1 - z) s + z c per channel;
 //                       W_o (s * silu(W_g h)).  State [width] fp32 per sequence slot.
-//   BlockAttention      grouped-query attention with biased q, k projections, values that ARE the keys before their rotation (no value
+//   BlockAttention      grouped-query attention with biased q, k projections, v = the un-rotated k (there is no value
 //                       projection), rotation in halves, weights sigmoid(scale q.k + b_h) -- no softmax, not normalised -- over the keys
-//                       of the query's own block of `block` positions, counted from position 0.  Cache: a ring of block + (step) - 1 rows
+//                       of the query's own block of `block` positions, aligned to position 0.  Cache: a ring of block + (step) - 1 rows
 //                       [rotated k | unrotated k] per slot.
 //   LatentAttention     (Sipazen.hpp) with the queries through a latent, stretched frequencies, neighbouring rotation pairs, no sink / gate.
 // Feed-forward: dense, clamped -- g = min(W_g h, L), u = clamp(W_u h, +-L), W_d (g sigmoid(alpha g) (u + 1)) -- or routed experts (MoE,

@@ -47,7 +47,7 @@ struct MIXER_CARD {
     double yarn_factor = 0.0, yarn_original = 0.0, yarn_fast = 0.0, yarn_slow = 0.0;
     // latent attention whose queries pass a latent of q_rank entries (RMS-normed) before their up-projection (0: projected directly)
     int q_rank = 0;
-    // sigmoid-weighted attention: a query sees the keys of its own block of `block` consecutive positions, counted from position 0 (0: all)
+    // sigmoid-weighted attention: a query sees the keys of its own block of `block` consecutive positions, aligned to position 0 (0: all)
     int block = 0;
     // channel-wise gated recurrence (minGRU): channels of the state
     int width = 0;

@@ -11,7 +11,7 @@ It shares no code with the library: it is what the GPU tests compare the framewo
     latent_attention:  c_q = norm(W_dq h), q = W_uq c_q = [plain | rotated] per head;  W_dkv h = [c | r], c <- norm(c), r rotated in
                        neighbouring pairs (2i, 2i+1) with stretched frequencies; k = [W_uk c | r], v = W_uv c; causal softmax; W_o
     dense ff:          g = min(W_g h, L), u = clamp(W_u h, -L, L);  W_d (g sigmoid(1.702 g) (u + 1))
-    experts:           s = sigmoid(W_r h); choice = s + correction; groups of neighbours ranked by the sum of their two largest choices, only
+    experts:           s = sigmoid(W_r h); choice = s + correction; contiguous groups ranked by the sum of their top-2 choices, only
                        the best `keep` groups stay; the `top` largest choices are taken; weights scale_r * s (not renormalised);
                        expert = W_d (silu(W_g h) * W_u h)
     logits = logit_scale * W_head norm(x; w_final)
@@ -88,7 +88,7 @@ def mingru(h, m, W, p, pos0=0, state=None):
 
 
 def block_attention(h, m, W, p):
-    """sigmoid-weighted attention inside blocks of mask.size positions counted from position 0; the values are the unrotated keys"""
+    """sigmoid-weighted attention inside blocks of mask.size positions aligned to position 0; v = un-rotated k"""
     T = h.shape[0]
     H, dk = m["heads"], m["dim"]
     G = m.get("kv_heads") or H
