@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(128) kf_moe_route_kernel(int32_t* __restrict__
     }
 }
 // few tokens (decode): routing and the dispatch tables in ONE block -- warps route the tokens, then thread i ranks entry i among the
-// earlier entries of its expert, thread e counts expert e, thread 0 scans the counts
+// earlier entries of its expert, the lanes of warp 0 count one expert each and scan the counts
 constexpr int kRouteSmall = 256;
 __global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __restrict__ idx, float* __restrict__ wgt, int32_t* __restrict__ offsets,
                                                                  int32_t* __restrict__ entry_slot, int32_t* __restrict__ slot_row,
@@ -353,13 +353,22 @@ __global__ void __launch_bounds__(256) kf_moe_route_small_kernel(int32_t* __rest
         srank[i] = r;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {  // offsets by a running count over the entries' experts: E may be large, n is small
-        int s = 0;
-        for (int e = 0; e < E; e++) {
-            offsets[e] = s;
-            for (int j = 0; j < n; j++) s += sidx[j] == e;
+    if (warp == 0) {  // offsets: lane l counts the entries of expert e0 + l, a scan over the lanes places them behind the experts before
+        int base = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            int c = 0;
+            for (int j = 0; j < n; j++) c += sidx[j] == e;  // e >= E matches nothing
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (e < E) offsets[e] = base + incl - c;
+            base += __shfl_sync(0xffffffffu, incl, 31);
         }
-        offsets[E] = s;
+        if (lane == 0) offsets[E] = base;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
